@@ -1,0 +1,121 @@
+/*
+ * spnb.h -- C ABI of the B200-native SPN joint log-likelihood engine (libspnb.so).
+ *
+ * This is the boundary a maintainer of the reference binds instead of the pieces listed beside
+ * each entry point (paths are inside the reference project).  Plain pointers and sizes only;
+ * every function returns 0 on success and a non-zero status otherwise, with a message available
+ * from spnb_last_error() (thread-local).  No function throws across the boundary.
+ *
+ * Life cycle:   spnb_compile (needs no GPU)  ->  spnb_plan_load  ->  spnb_execute_*  ->  spnb_plan_free
+ */
+#ifndef SPNB_H
+#define SPNB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct spnb_plan spnb_plan;
+
+/* Field-for-field the metadata of the reference's kernel descriptor
+ * (common/include/Kernel.h:39-126: queryType, target, batchSize, numFeatures, bytesPerFeature,
+ * numResults, bytesPerResult, dtype). */
+typedef struct spnb_kernel_info {
+  char kernel_name[256];
+  uint32_t query_type;        /* 0 = joint probability (common/include/Kernel.h:20) */
+  uint32_t target;            /* 2 = CUDA (common/include/Kernel.h:22) */
+  uint32_t batch_size;
+  uint32_t num_features;
+  uint32_t bytes_per_feature;
+  uint32_t num_results;
+  uint32_t bytes_per_result;
+  char dtype[16];             /* result dtype: "float32" (log space) or "float64" (linear space) */
+} spnb_kernel_info;
+
+/* Status codes. */
+enum {
+  SPNB_OK = 0,
+  SPNB_ERR_COMPILE = 1,       /* the reference throws std::runtime_error("COMPILATION ERROR") here */
+  SPNB_ERR_RUNTIME = 2,       /* ... and std::runtime_error("RUNTIME ERROR") here */
+  SPNB_ERR_ARGUMENT = 3,
+  SPNB_ERR_CUDA = 4
+};
+
+/*
+ * Compile an xspn query file into a plan file.
+ * Replaces spnc::spn_compiler::compileQuery (compiler/include/spnc.h:22-48, compiler/src/Driver.cpp:22-44)
+ * and everything behind it for the CUDA target (front end, lowering, cubin serialisation, linking:
+ * compiler/src/toolchain/CUDAGPUToolchain.cpp:29-105).
+ * Options are the reference's string->string option map (compiler/src/option/GlobalOptions.cpp:14-75);
+ * unknown keys are an error, as in compiler/src/option/Options.h:222-224.  "target" must be "CUDA".
+ * plan_out_path == NULL or "" lets the library pick a temporary file; the chosen path is returned in
+ * plan_path_out (capacity plan_path_cap bytes).  Needs no GPU (NVRTC cross-compiles for sm_100a).
+ */
+int spnb_compile(const char* query_path, const char* const* opt_keys, const char* const* opt_vals, int n_opts,
+                 const char* plan_out_path, char* plan_path_out, size_t plan_path_cap, spnb_kernel_info* info_out);
+
+/* Load a plan file written by spnb_compile.  Replaces the dlopen/dlsym of the generated kernel
+ * library (runtime/src/Executable.cpp:116-132).  Needs no GPU until the first execute. */
+int spnb_plan_load(const char* plan_path, spnb_plan** plan_out);
+
+int spnb_plan_info(const spnb_plan* plan, spnb_kernel_info* info_out);
+
+/* JSON with the planner's statistics (nodes per kind, edges, depth, algorithmic ops and bytes per
+ * sample, kernel strategy, registers).  Same role as the reference's graph statistics
+ * (mlir/lib/Dialect/LoSPN/Passes/LoSPNGraphStatsCollection.cpp:83-102).  Valid until the plan is freed. */
+const char* spnb_plan_stats_json(const spnb_plan* plan);
+
+/* The CUDA C++ source generated for the plan ("" for the interpreter strategy); what "dump-ir" shows. */
+const char* spnb_plan_source(const spnb_plan* plan);
+
+/*
+ * Evaluate n samples held in HOST memory: in = n x num_features x bytes_per_feature bytes, row-major,
+ * C-contiguous; out = n x bytes_per_result bytes.  Returns after the results are in out.
+ * Replaces spnc_rt::spn_runtime::execute -> Executable::executeGPU -> generated host stub
+ * (runtime/src/runtime.cpp:42-49, runtime/src/Executable.cpp:105-114) and the mgpu* wrappers it
+ * calls (runtime/wrappers/cuda/CUDARuntimeWrappers.cpp:56-153).  Runs on CUDA device 0 like the
+ * reference unless spnb_set_device was called; copies are chunked and overlapped with compute.
+ */
+int spnb_execute_host(spnb_plan* plan, size_t n, const void* in, void* out);
+
+/*
+ * Evaluate n samples already resident in DEVICE memory of `device`, asynchronously on `cuda_stream`
+ * (a cudaStream_t, NULL = default stream).  No counterpart in the reference, whose generated stub always
+ * allocates and copies (mlir/lib/Conversion/LoSPNtoGPU/GPUStructurePatterns.cpp:81-100,142-146).
+ */
+int spnb_execute_device(spnb_plan* plan, int device, size_t n, const void* d_in, void* d_out, void* cuda_stream);
+
+/*
+ * Evaluate n host-resident samples on several GPUs of this process: the batch is split into contiguous
+ * row blocks, one per listed device, the model tables are replicated on each device; no collective is
+ * involved.  If mean_ll_out != NULL it receives the mean log-likelihood over all n samples (summed in
+ * double on the host).  The reference runs on device 0 only (CUDARuntimeWrappers.cpp:36-54).
+ */
+int spnb_execute_sharded(spnb_plan* plan, const int* devices, int n_devices, size_t n, const void* in, void* out,
+                         double* mean_ll_out);
+
+/* Device used by spnb_execute_host (default 0). */
+int spnb_set_device(spnb_plan* plan, int device);
+
+/* Launch geometry the plan uses on `device`: CTAs, threads per CTA, dynamic shared memory bytes. */
+int spnb_launch_config(spnb_plan* plan, int device, int* grid, int* block, size_t* smem_bytes);
+
+/* Milliseconds the kernel(s) of the last spnb_execute_host call took on the device (CUDA events). */
+float spnb_last_kernel_ms(const spnb_plan* plan);
+
+void spnb_plan_free(spnb_plan* plan);
+
+/* Number of CUDA devices visible (0 if there is no driver). Backs SPNCompiler.isTargetSupported("CUDA")
+ * (compiler/src/Driver.cpp:47-59). */
+int spnb_device_count(void);
+
+const char* spnb_last_error(void);
+const char* spnb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPNB_H */

@@ -1,0 +1,30 @@
+// Emits one straight-line CUDA C++ kernel per model from the planned DAG (compiled by NVRTC for
+// sm_100a).  This replaces the reference's LoSPN -> GPU dialect -> NVVM -> PTX lowering
+// (mlir/lib/Conversion/LoSPNtoGPU/GPUStructurePatterns.cpp:28-152, GPUNodePatterns.cpp:16-509).
+#pragma once
+#include <string>
+
+#include "plan.h"
+
+namespace spnb {
+
+struct EmitOptions {
+  int tile = 128;          // threads per CTA = samples per tile
+  int minBlocksPerSM = 4;  // __launch_bounds__ hint
+  int syncEvery = 0;       // CTA barrier every this many DAG nodes (0 = never): keeps the warps of a CTA
+                           // on the same stretch of the instruction stream
+  int smemTableLimit = 64 * 1024;  // leaf tables larger than this stay in global memory
+};
+
+struct EmitInfo {
+  std::string kernelName;
+  int tile = 0;
+  int inputStride = 0;      // floats between two features of one sample in shared memory (tile + 1)
+  size_t dynamicSmemBytes = 0;
+  bool tablesInSmem = false;
+  size_t tableEntries = 0;
+};
+
+std::string emitCuda(const Plan& plan, const EmitOptions& opt, EmitInfo* info);
+
+}  // namespace spnb

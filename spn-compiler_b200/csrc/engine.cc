@@ -1,0 +1,578 @@
+#include "engine.h"
+
+#include <cuda.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <set>
+#include <sstream>
+#include <stdexcept>
+#include <thread>
+
+#include "interp.h"
+#include "jit.h"
+
+namespace spnb {
+
+namespace {
+
+[[noreturn]] void fail(const std::string& m) { throw std::runtime_error(m); }
+
+#define CUDA_OK(expr)                                                                              \
+  do {                                                                                             \
+    cudaError_t e_ = (expr);                                                                       \
+    if (e_ != cudaSuccess)                                                                         \
+      fail(std::string("CUDA error: ") + cudaGetErrorString(e_) + " at " #expr);                   \
+  } while (0)
+
+// ---- driver API, resolved through the runtime so that the library links without libcuda ---------
+struct Driver {
+  decltype(&cuModuleLoadData) moduleLoadData = nullptr;
+  decltype(&cuModuleUnload) moduleUnload = nullptr;
+  decltype(&cuModuleGetFunction) moduleGetFunction = nullptr;
+  decltype(&cuFuncSetAttribute) funcSetAttribute = nullptr;
+  decltype(&cuLaunchKernel) launchKernel = nullptr;
+  decltype(&cuOccupancyMaxActiveBlocksPerMultiprocessor) occupancy = nullptr;
+  decltype(&cuGetErrorString) getErrorString = nullptr;
+
+  static Driver& get() {
+    static Driver d;
+    static std::once_flag once;
+    std::call_once(once, [] {
+      auto load = [](const char* name, void** fn) {
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !*fn)
+          fail(std::string("cannot resolve CUDA driver entry point ") + name);
+      };
+      load("cuModuleLoadData", (void**)&d.moduleLoadData);
+      load("cuModuleUnload", (void**)&d.moduleUnload);
+      load("cuModuleGetFunction", (void**)&d.moduleGetFunction);
+      load("cuFuncSetAttribute", (void**)&d.funcSetAttribute);
+      load("cuLaunchKernel", (void**)&d.launchKernel);
+      load("cuOccupancyMaxActiveBlocksPerMultiprocessor", (void**)&d.occupancy);
+      load("cuGetErrorString", (void**)&d.getErrorString);
+    });
+    return d;
+  }
+  void check(CUresult r, const char* what) {
+    if (r == CUDA_SUCCESS) return;
+    const char* s = nullptr;
+    if (getErrorString) getErrorString(r, &s);
+    fail(std::string("CUDA driver error: ") + (s ? s : "unknown") + " in " + what);
+  }
+};
+
+bool parseBool(const std::string& v) {
+  std::string l = v;
+  std::transform(l.begin(), l.end(), l.begin(), ::tolower);
+  return l == "true" || l == "yes";  // compiler/src/option/Options.cpp:79-82 of the reference
+}
+
+int dtypeCode(const FeatureType& t) {
+  if (t.kind == InKind::Float) return t.bits == 32 ? DT_F32 : DT_F64;
+  bool u = t.kind == InKind::UInt;
+  switch (t.bits) {
+    case 8: return u ? DT_U8 : DT_I8;
+    case 16: return u ? DT_U16 : DT_I16;
+    case 32: return u ? DT_U32 : DT_I32;
+    default: return u ? DT_U64 : DT_I64;
+  }
+}
+
+// ---- plan file -----------------------------------------------------------------------------------
+const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '2'};
+
+struct Writer {
+  std::vector<uint8_t> b;
+  void raw(const void* p, size_t n) { b.insert(b.end(), (const uint8_t*)p, (const uint8_t*)p + n); }
+  void u64(uint64_t v) { raw(&v, 8); }
+  void str(const std::string& s) { u64(s.size()); raw(s.data(), s.size()); }
+  void blob(const void* p, size_t n) { u64(n); raw(p, n); }
+};
+struct Reader {
+  const uint8_t* p; size_t n; size_t o = 0;
+  void need(size_t k) { if (k > n - o) fail("plan file truncated"); }
+  uint64_t u64() { need(8); uint64_t v; std::memcpy(&v, p + o, 8); o += 8; return v; }
+  std::string str() { uint64_t k = u64(); need(k); std::string s((const char*)p + o, k); o += k; return s; }
+  std::vector<uint8_t> blob() { uint64_t k = u64(); need(k); std::vector<uint8_t> v(p + o, p + o + k); o += k; return v; }
+};
+
+std::vector<uint8_t> readFile(const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) fail("Could not open file " + path);
+  return std::vector<uint8_t>((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+}
+
+std::string makeStatsJson(const Plan& p, Strategy s, const EmitInfo& ei, int regs, int spill, int interpSlots) {
+  std::ostringstream o;
+  std::string base = p.stats.toJson();
+  base.pop_back();
+  o << base << ",\"log_space\":" << (p.logSpace ? "true" : "false") << ",\"strategy\":\""
+    << (s == kUnrolled ? "unrolled" : "interpreter") << "\",\"tile\":" << ei.tile << ",\"registers\":" << regs
+    << ",\"spill_bytes\":" << spill << ",\"smem_bytes\":" << ei.dynamicSmemBytes << ",\"interp_slots\":" << interpSlots
+    << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
+  return o.str();
+}
+
+void parallelCopy(void* dst, const void* src, size_t bytes) {
+  const size_t kMin = 4u << 20;
+  unsigned nt = (unsigned)std::min<size_t>(4, bytes / kMin);
+  if (nt <= 1) {
+    std::memcpy(dst, src, bytes);
+    return;
+  }
+  std::vector<std::thread> th;
+  size_t per = (bytes / nt + 63) & ~size_t(63);
+  for (unsigned t = 0; t < nt; ++t) {
+    size_t lo = (size_t)t * per, hi = std::min(bytes, lo + per);
+    if (lo >= hi) break;
+    th.emplace_back([=] { std::memcpy((char*)dst + lo, (const char*)src + lo, hi - lo); });
+  }
+  for (auto& t : th) t.join();
+}
+
+}  // namespace
+
+// ---- options --------------------------------------------------------------------------------------
+Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv) {
+  static const std::set<std::string> ignored = {
+      "gpu-shared-mem", "search-paths", "cpu-vectorize", "vector-library", "use-shuffle", "irOptLevel", "mcOptLevel",
+      "maxTaskSize", "slp-max-attempts", "slp-max-successful-iterations", "slp-max-node-size", "slp-max-look-ahead",
+      "slp-reorder-dfs", "slp-allow-duplicate-elements", "slp-allow-topological-mixing", "slp-use-xor-chains",
+      "delete-temps", "opt-repr", "stopAfter"};
+  Options o;
+  o.raw = kv;
+  bool haveTarget = false;
+  for (auto& p : kv) {
+    const std::string& k = p.first;
+    const std::string& v = p.second;
+    if (k == "target") {
+      haveTarget = true;
+      if (v == "CPU") fail("Target was 'CPU', but this engine only implements the CUDA target");
+      if (v != "CUDA") fail("Unknown value '" + v + "' for option target");
+    } else if (k == "use-log-space") o.logSpace = parseBool(v);
+    else if (k == "dump-ir") o.dumpIR = parseBool(v);
+    else if (k == "collect-graph-stats") o.collectStats = parseBool(v);
+    else if (k == "graph-stats-file") o.statsFile = v;
+    else if (k == "optLevel") o.optLevel = std::atoi(v.c_str());
+    else if (k == "spnb-kernel") {
+      if (v != "auto" && v != "unrolled" && v != "interp") fail("Unknown value '" + v + "' for option spnb-kernel");
+      o.kernelMode = v;
+    } else if (k == "spnb-tile") o.tile = std::atoi(v.c_str());
+    else if (k == "spnb-min-blocks") o.minBlocks = std::atoi(v.c_str());
+    else if (k == "spnb-sync-every") o.syncEvery = std::atoi(v.c_str());
+    else if (k == "spnb-unroll-limit") o.unrollLimit = std::atoi(v.c_str());
+    else if (k == "spnb-max-registers") o.maxRegisters = std::atoi(v.c_str());
+    else if (!ignored.count(k)) fail("Unknown compile option " + k);
+  }
+  if (!haveTarget) fail("Missing required option target");
+  if (o.tile && (o.tile < 32 || o.tile > 1024 || o.tile % 32)) fail("spnb-tile must be a multiple of 32 in [32, 1024]");
+  return o;
+}
+
+// ---- compile --------------------------------------------------------------------------------------
+std::string Engine::compile(const std::string& queryPath, const Options& opt, const std::string& planPathIn,
+                            KernelMeta* metaOut) {
+  std::vector<uint8_t> xspn = readFile(queryPath);
+  Model m = readXspnBytes(xspn.data(), xspn.size());
+  if (!m.isQuery) fail("Cannot compile raw models");  // SPFlowToMLIRDeserializer.cpp:43-45
+  validateModel(m);
+  Plan plan = buildPlan(m, opt.logSpace);
+
+  Strategy strat;
+  const int64_t size = plan.stats.nodes + plan.stats.sumEdges + plan.stats.productEdges;
+  if (opt.kernelMode == "unrolled") strat = kUnrolled;
+  else if (opt.kernelMode == "interp") strat = kInterpreter;
+  else strat = size <= opt.unrollLimit ? kUnrolled : kInterpreter;
+  if (strat == kInterpreter && !opt.logSpace)
+    fail("The interpreter kernel evaluates in log space only; pass use-log-space=true for a DAG of this size");
+
+  EmitInfo ei;
+  std::string source;
+  JitResult jr;
+  if (strat == kUnrolled) {
+    EmitOptions eo;
+    if (opt.tile) eo.tile = opt.tile;
+    if (opt.minBlocks) eo.minBlocksPerSM = opt.minBlocks;
+    eo.syncEvery = opt.syncEvery;
+    source = emitCuda(plan, eo, &ei);
+    if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
+    jr = jitCompile(source, m.name, opt.optLevel, opt.maxRegisters);
+  } else {
+    ei.tile = opt.tile;  // 0: chosen at load time from the shared-memory budget
+  }
+
+  std::string stats = makeStatsJson(plan, strat, ei, jr.registers, jr.spillBytes, plan.numSlots);
+  if (opt.dumpIR) {
+    std::fprintf(stderr, "// *** spnb plan statistics ***\n%s\n", stats.c_str());
+    if (!source.empty()) std::fprintf(stderr, "// *** generated CUDA source ***\n%s\n// *** NVRTC log ***\n%s\n", source.c_str(), jr.log.c_str());
+  }
+  if (opt.collectStats) {
+    std::ofstream f(opt.statsFile);
+    f << stats << "\n";
+  }
+
+  std::string planPath = planPathIn;
+  if (planPath.empty()) {
+    const char* tmp = std::getenv("TMPDIR");
+    std::string templ = std::string(tmp && *tmp ? tmp : "/tmp") + "/spnbXXXXXX.plan";
+    std::vector<char> buf(templ.begin(), templ.end());
+    buf.push_back(0);
+    int fd = mkstemps(buf.data(), 5);
+    if (fd < 0) fail("Could not create a temporary plan file");
+    close(fd);
+    planPath = buf.data();
+  }
+  Writer w;
+  w.raw(kMagic, 8);
+  w.u64(opt.raw.size());
+  for (auto& kv : opt.raw) { w.str(kv.first); w.str(kv.second); }
+  w.u64((uint64_t)strat);
+  w.u64((uint64_t)ei.tile);
+  w.u64((uint64_t)ei.dynamicSmemBytes);
+  w.u64((uint64_t)(jr.registers + 1));
+  w.u64((uint64_t)(jr.spillBytes + 1));
+  w.blob(xspn.data(), xspn.size());
+  w.str(source);
+  w.blob(jr.cubin.data(), jr.cubin.size());
+  {
+    std::ofstream f(planPath, std::ios::binary | std::ios::trunc);
+    if (!f) fail("Could not write plan file " + planPath);
+    f.write((const char*)w.b.data(), (std::streamsize)w.b.size());
+  }
+  if (metaOut) {
+    metaOut->kernelName = m.name;
+    metaOut->batchSize = (uint32_t)std::max(m.batchSize, 0);
+    metaOut->numFeatures = (uint32_t)m.numFeatures;
+    metaOut->bytesPerFeature = (uint32_t)m.ftype.bytes();
+    metaOut->bytesPerResult = opt.logSpace ? 4 : 8;
+    metaOut->dtype = opt.logSpace ? "float32" : "float64";
+  }
+  return planPath;
+}
+
+// ---- per-device state -------------------------------------------------------------------------------
+struct Engine::DeviceState {
+  int device = 0;
+  int smCount = 0;
+  CUmodule module = nullptr;
+  CUfunction fn = nullptr;
+  void* dTab = nullptr;
+  void* dLut = nullptr;
+  int* dProg = nullptr;
+  int* dBreaks = nullptr;
+  int4* dMeta = nullptr;
+  int grid = 0, block = 0;
+  size_t smem = 0;
+  InterpArgs ia{};
+  // host path
+  static constexpr int kBuf = 3;
+  cudaStream_t streams[kBuf] = {nullptr, nullptr, nullptr};
+  void* hIn[kBuf] = {nullptr, nullptr, nullptr};
+  void* dIn[kBuf] = {nullptr, nullptr, nullptr};
+  size_t stageBytes = 0;
+  void* dOut = nullptr;
+  void* hOut = nullptr;
+  size_t outBytes = 0;
+
+  ~DeviceState() {
+    cudaSetDevice(device);
+    for (int i = 0; i < kBuf; ++i) {
+      if (streams[i]) cudaStreamDestroy(streams[i]);
+      if (hIn[i]) cudaFreeHost(hIn[i]);
+      if (dIn[i]) cudaFree(dIn[i]);
+    }
+    if (dOut) cudaFree(dOut);
+    if (hOut) cudaFreeHost(hOut);
+    if (dTab) cudaFree(dTab);
+    if (dLut) cudaFree(dLut);
+    if (dProg) cudaFree(dProg);
+    if (dBreaks) cudaFree(dBreaks);
+    if (dMeta) cudaFree(dMeta);
+    if (module) Driver::get().moduleUnload(module);
+  }
+};
+
+Engine::~Engine() = default;
+
+std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
+  std::vector<uint8_t> file = readFile(planPath);
+  if (file.size() < 8 || std::memcmp(file.data(), kMagic, 8) != 0) fail("Not a spnb plan file: " + planPath);
+  Reader r{file.data(), file.size(), 8};
+  std::vector<std::pair<std::string, std::string>> kv;
+  uint64_t nopt = r.u64();
+  for (uint64_t i = 0; i < nopt; ++i) {
+    std::string k = r.str();
+    std::string v = r.str();
+    kv.emplace_back(k, v);
+  }
+  Options opt = parseOptions(kv);
+  std::unique_ptr<Engine> e(new Engine());
+  e->strategy_ = (Strategy)r.u64();
+  e->emitInfo_.tile = (int)r.u64();
+  e->emitInfo_.dynamicSmemBytes = (size_t)r.u64();
+  int regs = (int)r.u64() - 1;
+  int spill = (int)r.u64() - 1;
+  std::vector<uint8_t> xspn = r.blob();
+  e->source_ = r.str();
+  std::vector<uint8_t> cubin = r.blob();
+  e->cubin_.assign(cubin.begin(), cubin.end());
+  e->model_ = readXspnBytes(xspn.data(), xspn.size());
+  e->plan_ = buildPlan(e->model_, opt.logSpace);
+  e->emitInfo_.kernelName = "spnb_kernel";
+  e->interpTile_ = e->emitInfo_.tile;
+  e->meta_.kernelName = e->model_.name;
+  e->meta_.batchSize = (uint32_t)std::max(e->model_.batchSize, 0);
+  e->meta_.numFeatures = (uint32_t)e->model_.numFeatures;
+  e->meta_.bytesPerFeature = (uint32_t)e->model_.ftype.bytes();
+  e->meta_.bytesPerResult = opt.logSpace ? 4 : 8;
+  e->meta_.dtype = opt.logSpace ? "float32" : "float64";
+  e->statsJson_ = makeStatsJson(e->plan_, e->strategy_, e->emitInfo_, regs, spill, e->plan_.numSlots);
+  return e;
+}
+
+Engine::DeviceState& Engine::state(int device) {
+  std::lock_guard<std::mutex> lock(mu_);
+  auto it = dev_.find(device);
+  if (it != dev_.end()) return *it->second;
+  int count = 0;
+  cudaError_t ce = cudaGetDeviceCount(&count);
+  if (ce != cudaSuccess || count == 0)
+    fail("No CUDA device available: the spnb engine has no CPU fallback");
+  if (device < 0 || device >= count) fail("CUDA device " + std::to_string(device) + " does not exist");
+  CUDA_OK(cudaSetDevice(device));
+  CUDA_OK(cudaFree(nullptr));
+  std::unique_ptr<DeviceState> st(new DeviceState());
+  st->device = device;
+  cudaDeviceProp prop;
+  CUDA_OK(cudaGetDeviceProperties(&prop, device));
+  st->smCount = prop.multiProcessorCount;
+  const Plan& p = plan_;
+  auto upload = [&](const void* src, size_t bytes) -> void* {
+    void* d = nullptr;
+    CUDA_OK(cudaMalloc(&d, std::max<size_t>(bytes, 16)));
+    if (bytes) CUDA_OK(cudaMemcpy(d, src, bytes, cudaMemcpyHostToDevice));
+    return d;
+  };
+  if (p.logSpace) st->dTab = upload(p.tabF32.data(), p.tabF32.size() * 4);
+  else st->dTab = upload(p.tabF64.data(), p.tabF64.size() * 8);
+  st->dLut = upload(p.lut.data(), p.lut.size());
+  if (strategy_ == kUnrolled) {
+    Driver& drv = Driver::get();
+    drv.check(drv.moduleLoadData(&st->module, cubin_.data()), "cuModuleLoadData");
+    drv.check(drv.moduleGetFunction(&st->fn, st->module, "spnb_kernel"), "cuModuleGetFunction");
+    st->block = emitInfo_.tile;
+    st->smem = emitInfo_.dynamicSmemBytes;
+    if (st->smem > 48 * 1024)
+      drv.check(drv.funcSetAttribute(st->fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)st->smem),
+                "cuFuncSetAttribute");
+    int perSM = 0;
+    drv.check(drv.occupancy(&perSM, st->fn, st->block, st->smem), "cuOccupancyMaxActiveBlocksPerMultiprocessor");
+    if (perSM < 1) fail("Generated kernel does not fit on one SM");
+    st->grid = perSM * st->smCount;
+  } else {
+    std::vector<int4> meta(p.features.size());
+    for (size_t f = 0; f < meta.size(); ++f)
+      meta[f] = make_int4(p.features[f].lo, p.features[f].domain, p.features[f].codeSlot, p.features[f].valueSlot);
+    st->dProg = (int*)upload(p.prog.data(), p.prog.size() * 4);
+    st->dBreaks = (int*)upload(p.groupBreaks.data(), p.groupBreaks.size() * 4);
+    st->dMeta = (int4*)upload(meta.data(), meta.size() * sizeof(int4));
+    st->ia.prog = st->dProg;
+    st->ia.tab = (const float*)st->dTab;
+    st->ia.lut = (const unsigned char*)st->dLut;
+    st->ia.breaks = st->dBreaks;
+    st->ia.featureMeta = st->dMeta;
+    st->ia.numFeatures = (int)p.features.size();
+    st->ia.numValueSlots = p.numValueSlots;
+    st->ia.numCodeSlots = p.numCodeSlots;
+    st->ia.numSlots = p.numSlots;
+    st->ia.marginal = p.marginal ? 1 : 0;
+    // largest tile whose inputs and value slots fit into the shared memory of one SM
+    const size_t budget = (size_t)prop.sharedMemPerBlockOptin;
+    int tile = interpTile_ ? interpTile_ : 256;
+    while (tile > 32 && interpSmemBytes(st->ia, tile) > budget) tile -= 32;
+    if (interpSmemBytes(st->ia, tile) > budget)
+      fail("Model needs " + std::to_string(p.numSlots) + " live values per sample: too many for the interpreter's shared-memory slots");
+    // prefer two or more resident CTAs per SM when the tile allows it
+    if (!interpTile_)
+      while (tile > 64 && interpSmemBytes(st->ia, tile) > budget / 2 && interpSmemBytes(st->ia, tile / 2) <= budget / 2) tile /= 2;
+    st->block = tile;
+    st->smem = interpSmemBytes(st->ia, tile);
+    int perSM = 0;
+    CUDA_OK(interpOccupancy(dtypeCode(p.ftype), tile, st->smem, &perSM));
+    if (perSM < 1) fail("Interpreter kernel does not fit on one SM");
+    st->grid = perSM * st->smCount;
+  }
+  auto ins = dev_.emplace(device, std::move(st));
+  return *ins.first->second;
+}
+
+void Engine::launchConfig(int device, int* grid, int* block, size_t* smem) {
+  DeviceState& st = state(device);
+  if (grid) *grid = st.grid;
+  if (block) *block = st.block;
+  if (smem) *smem = st.smem;
+}
+
+void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cudaStream_t stream) {
+  if (n == 0) return;
+  const size_t tiles = (n + (size_t)st.block - 1) / (size_t)st.block;
+  const int grid = (int)std::min<size_t>(tiles, (size_t)st.grid);
+  if (strategy_ == kUnrolled) {
+    unsigned long long nn = n;
+    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut};
+    Driver& drv = Driver::get();
+    drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
+              "cuLaunchKernel");
+  } else {
+    CUDA_OK(interpLaunch(st.ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
+  }
+}
+
+void Engine::executeDevice(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream) {
+  DeviceState& st = state(device);
+  int cur = -1;
+  CUDA_OK(cudaGetDevice(&cur));
+  if (cur != device) CUDA_OK(cudaSetDevice(device));
+  launch(st, n, dIn, dOut, stream);
+  if (cur != device && cur >= 0) CUDA_OK(cudaSetDevice(cur));
+}
+
+// Host-resident batch on one device: chunks are copied to pinned staging (unless the caller's
+// buffer is already pinned), sent with cudaMemcpyAsync and evaluated on rotating streams so that
+// copy-in, kernel and copy-out of neighbouring chunks overlap.
+void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, float* kernelMs) {
+  if (kernelMs) *kernelMs = 0.f;
+  if (n == 0) return;
+  DeviceState& st = state(device);
+  CUDA_OK(cudaSetDevice(device));
+  const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature;
+  const size_t resBytes = meta_.bytesPerResult;
+  size_t chunkRows = std::max<size_t>((size_t)(48u << 20) / std::max<size_t>(rowBytes, 1), 4096);
+  chunkRows = (chunkRows / (size_t)st.block + 1) * (size_t)st.block;
+  chunkRows = std::min(chunkRows, n);
+  const size_t nChunks = (n + chunkRows - 1) / chunkRows;
+
+  cudaPointerAttributes ai{}, ao{};
+  bool inPinned = cudaPointerGetAttributes(&ai, in) == cudaSuccess && ai.type == cudaMemoryTypeHost;
+  bool outPinned = cudaPointerGetAttributes(&ao, out) == cudaSuccess && ao.type == cudaMemoryTypeHost;
+  cudaGetLastError();
+
+  const int nbuf = (int)std::min<size_t>(DeviceState::kBuf, nChunks);
+  const size_t needStage = chunkRows * rowBytes;
+  if (needStage > st.stageBytes) {
+    for (int b = 0; b < DeviceState::kBuf; ++b) {
+      if (st.hIn[b]) { cudaFreeHost(st.hIn[b]); st.hIn[b] = nullptr; }
+      if (st.dIn[b]) { cudaFree(st.dIn[b]); st.dIn[b] = nullptr; }
+    }
+    st.stageBytes = 0;
+  }
+  for (int b = 0; b < nbuf; ++b) {
+    if (!st.streams[b]) CUDA_OK(cudaStreamCreateWithFlags(&st.streams[b], cudaStreamNonBlocking));
+    if (!st.dIn[b]) CUDA_OK(cudaMalloc(&st.dIn[b], needStage));
+    if (!inPinned && !st.hIn[b]) CUDA_OK(cudaHostAlloc(&st.hIn[b], needStage, cudaHostAllocDefault));
+  }
+  st.stageBytes = std::max(st.stageBytes, needStage);
+  if (n * resBytes > st.outBytes) {
+    if (st.dOut) cudaFree(st.dOut);
+    if (st.hOut) cudaFreeHost(st.hOut);
+    st.dOut = st.hOut = nullptr;
+    CUDA_OK(cudaMalloc(&st.dOut, n * resBytes));
+    st.outBytes = n * resBytes;
+  }
+  if (!outPinned && !st.hOut) CUDA_OK(cudaHostAlloc(&st.hOut, st.outBytes, cudaHostAllocDefault));
+
+  std::vector<cudaEvent_t> k0(nChunks), k1(nChunks), done(nChunks);
+  for (size_t c = 0; c < nChunks; ++c) {
+    CUDA_OK(cudaEventCreate(&k0[c]));
+    CUDA_OK(cudaEventCreate(&k1[c]));
+    CUDA_OK(cudaEventCreateWithFlags(&done[c], cudaEventDisableTiming));
+  }
+  char* hostOut = outPinned ? (char*)out : (char*)st.hOut;
+  size_t drained = 0;  // chunks whose results have been handed to the caller
+  auto drain = [&](size_t upto) {
+    for (; drained < upto; ++drained) {
+      CUDA_OK(cudaEventSynchronize(done[drained]));
+      if (!outPinned) {
+        size_t r0 = drained * chunkRows, rows = std::min(chunkRows, n - r0);
+        std::memcpy((char*)out + r0 * resBytes, hostOut + r0 * resBytes, rows * resBytes);
+      }
+    }
+  };
+  for (size_t c = 0; c < nChunks; ++c) {
+    const int b = (int)(c % (size_t)nbuf);
+    const size_t r0 = c * chunkRows, rows = std::min(chunkRows, n - r0);
+    if (c >= (size_t)nbuf) drain(c - nbuf + 1);  // buffer b is free once its previous chunk is done
+    const char* src = (const char*)in + r0 * rowBytes;
+    if (!inPinned) {
+      parallelCopy(st.hIn[b], src, rows * rowBytes);
+      src = (const char*)st.hIn[b];
+    }
+    cudaStream_t s = st.streams[b];
+    CUDA_OK(cudaMemcpyAsync(st.dIn[b], src, rows * rowBytes, cudaMemcpyHostToDevice, s));
+    CUDA_OK(cudaEventRecord(k0[c], s));
+    launch(st, rows, st.dIn[b], (char*)st.dOut + r0 * resBytes, s);
+    CUDA_OK(cudaEventRecord(k1[c], s));
+    CUDA_OK(cudaMemcpyAsync(hostOut + r0 * resBytes, (char*)st.dOut + r0 * resBytes, rows * resBytes,
+                            cudaMemcpyDeviceToHost, s));
+    CUDA_OK(cudaEventRecord(done[c], s));
+  }
+  drain(nChunks);
+  float total = 0.f;
+  for (size_t c = 0; c < nChunks; ++c) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, k0[c], k1[c]) == cudaSuccess) total += ms;
+    cudaEventDestroy(k0[c]);
+    cudaEventDestroy(k1[c]);
+    cudaEventDestroy(done[c]);
+  }
+  if (kernelMs) *kernelMs = total;
+}
+
+void Engine::executeHost(size_t n, const void* in, void* out) {
+  float ms = 0.f;
+  runHostOnDevice(hostDevice_, n, in, out, &ms);
+  lastKernelMs_ = ms;
+}
+
+void Engine::executeSharded(const int* devices, int nDevices, size_t n, const void* in, void* out, double* meanOut) {
+  if (nDevices <= 0) fail("executeSharded needs at least one device");
+  const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature;
+  const size_t resBytes = meta_.bytesPerResult;
+  // contiguous row blocks, sizes rounded to 1024 samples so that every shard starts tile-aligned
+  size_t per = (n + (size_t)nDevices - 1) / (size_t)nDevices;
+  per = (per + 1023) / 1024 * 1024;
+  for (int i = 0; i < nDevices; ++i) state(devices[i]);  // create states up front, serially
+  std::vector<std::thread> th;
+  std::vector<std::string> errors((size_t)nDevices);
+  std::vector<float> ms((size_t)nDevices, 0.f);
+  for (int i = 0; i < nDevices; ++i) {
+    size_t r0 = std::min(n, (size_t)i * per), r1 = std::min(n, r0 + per);
+    if (r0 >= r1) continue;
+    th.emplace_back([&, i, r0, r1] {
+      try {
+        runHostOnDevice(devices[i], r1 - r0, (const char*)in + r0 * rowBytes, (char*)out + r0 * resBytes, &ms[(size_t)i]);
+      } catch (const std::exception& e) {
+        errors[(size_t)i] = e.what();
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  for (auto& e : errors)
+    if (!e.empty()) fail(e);
+  lastKernelMs_ = *std::max_element(ms.begin(), ms.end());
+  if (meanOut) {
+    double s = 0.0;
+    if (resBytes == 4) for (size_t i = 0; i < n; ++i) s += ((const float*)out)[i];
+    else for (size_t i = 0; i < n; ++i) s += ((const double*)out)[i];
+    *meanOut = n ? s / (double)n : 0.0;
+  }
+}
+
+}  // namespace spnb

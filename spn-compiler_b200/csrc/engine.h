@@ -1,0 +1,87 @@
+// Engine: compile (xspn -> plan file) and execute (plan file -> per-sample log-likelihoods on
+// one or several GPUs).  Everything above the C ABI in c_api.cc goes through this class.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "emit.h"
+#include "model.h"
+#include "plan.h"
+
+namespace spnb {
+
+struct KernelMeta {
+  std::string kernelName;
+  uint32_t queryType = 0, target = 2, batchSize = 1, numFeatures = 0, bytesPerFeature = 0, numResults = 1,
+           bytesPerResult = 4;
+  std::string dtype = "float32";
+};
+
+// Compile options: the reference's keys (compiler/src/option/GlobalOptions.cpp:14-75) plus the
+// engine's own "spnb-*" keys.
+struct Options {
+  bool logSpace = false;       // "use-log-space" (reference default false; its Python layer passes true)
+  bool dumpIR = false;         // "dump-ir": print the generated CUDA source and the plan statistics
+  bool collectStats = false;   // "collect-graph-stats"
+  std::string statsFile = "/tmp/stats.json";
+  int optLevel = 3;            // "optLevel"
+  std::string kernelMode = "auto";  // "spnb-kernel": auto | unrolled | interp
+  int tile = 0;                // "spnb-tile": threads per CTA (0 = default)
+  int minBlocks = 0;           // "spnb-min-blocks": __launch_bounds__ hint of the generated kernel
+  int syncEvery = 0;           // "spnb-sync-every"
+  int unrollLimit = 20000;     // "spnb-unroll-limit": nodes + edges up to which a DAG is unrolled
+  int maxRegisters = 0;        // "spnb-max-registers"
+  std::vector<std::pair<std::string, std::string>> raw;
+};
+
+Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv);
+
+enum Strategy : int32_t { kUnrolled = 0, kInterpreter = 1 };
+
+class Engine {
+ public:
+  // Compile `queryPath` into `planPath` (empty: a fresh temporary file is chosen and returned).
+  static std::string compile(const std::string& queryPath, const Options& opt, const std::string& planPath,
+                             KernelMeta* meta);
+  static std::unique_ptr<Engine> load(const std::string& planPath);
+  ~Engine();
+
+  const KernelMeta& meta() const { return meta_; }
+  const std::string& statsJson() const { return statsJson_; }
+  const std::string& source() const { return source_; }
+
+  void executeHost(size_t n, const void* in, void* out);
+  void executeDevice(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream);
+  void executeSharded(const int* devices, int nDevices, size_t n, const void* in, void* out, double* meanOut);
+  void setDevice(int device) { hostDevice_ = device; }
+  void launchConfig(int device, int* grid, int* block, size_t* smem);
+  float lastKernelMs() const { return lastKernelMs_; }
+
+ private:
+  struct DeviceState;
+  Engine() = default;
+  DeviceState& state(int device);
+  void launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cudaStream_t stream);
+  void runHostOnDevice(int device, size_t n, const void* in, void* out, float* kernelMs);
+
+  Model model_;
+  Plan plan_;
+  KernelMeta meta_;
+  Strategy strategy_ = kUnrolled;
+  EmitInfo emitInfo_;
+  int interpTile_ = 0;
+  std::string source_;
+  std::vector<char> cubin_;
+  std::string statsJson_;
+  int hostDevice_ = 0;
+  float lastKernelMs_ = 0.f;
+  std::mutex mu_;
+  std::map<int, std::unique_ptr<DeviceState>> dev_;
+};
+
+}  // namespace spnb

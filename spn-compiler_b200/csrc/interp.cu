@@ -1,0 +1,223 @@
+// Table-driven interpreter kernel for DAGs too large to unroll: one thread per sample, the op
+// stream is walked by every thread in lock step (all control flow is warp-uniform), values live
+// in shared-memory slots [slot][thread] assigned by liveness in the planner.
+//
+// Replaces what the reference does for oversized graphs, namely splitting the task into
+// partitions with feature-major [k x N] intermediates in global memory
+// (mlir/lib/Dialect/LoSPN/Passes/LoSPNTaskPartitioner.cpp:36-148); here intermediates never
+// leave the SM.  Arithmetic is the same log-space formulation as the generated kernels: base-2
+// logarithms, products are adds, sums are max-shifted log-sum-exp on the SFU.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "interp.h"
+
+namespace spnb {
+
+namespace {
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename T>
+__device__ __forceinline__ int toIntSat(T v);
+template <> __device__ __forceinline__ int toIntSat<float>(float v) { return __float2int_rz(v); }
+template <> __device__ __forceinline__ int toIntSat<double>(double v) { return __double2int_rz(v); }
+template <> __device__ __forceinline__ int toIntSat<int8_t>(int8_t v) { return v; }
+template <> __device__ __forceinline__ int toIntSat<uint8_t>(uint8_t v) { return v; }
+template <> __device__ __forceinline__ int toIntSat<int16_t>(int16_t v) { return v; }
+template <> __device__ __forceinline__ int toIntSat<uint16_t>(uint16_t v) { return v; }
+template <> __device__ __forceinline__ int toIntSat<int32_t>(int32_t v) { return v; }
+template <> __device__ __forceinline__ int toIntSat<uint32_t>(uint32_t v) { return v > 2147483647u ? 2147483647 : (int)v; }
+template <> __device__ __forceinline__ int toIntSat<int64_t>(int64_t v) {
+  return v > 2147483647ll ? 2147483647 : (v < -2147483648ll ? (-2147483647 - 1) : (int)v);
+}
+template <> __device__ __forceinline__ int toIntSat<uint64_t>(uint64_t v) { return v > 2147483647ull ? 2147483647 : (int)v; }
+
+template <typename T> struct IsFloat { static constexpr bool value = false; };
+template <> struct IsFloat<float> { static constexpr bool value = true; };
+template <> struct IsFloat<double> { static constexpr bool value = true; };
+
+// Shared memory: [fm int4 x F][xs float x NV*SX][cs int x NC*SX][vals float x nslots*TILE]
+template <typename in_t>
+__global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* __restrict__ in, float* __restrict__ out,
+                                                       unsigned long long n) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const unsigned tid = threadIdx.x;
+  const unsigned TILE = blockDim.x;
+  const unsigned SX = TILE + 1;
+  const unsigned F = a.numFeatures;
+  int4* fm = reinterpret_cast<int4*>(smem_raw);
+  float* xs = reinterpret_cast<float*>(smem_raw + (size_t)F * 16);
+  int* cs = reinterpret_cast<int*>(xs + (size_t)a.numValueSlots * SX);
+  float* vals = reinterpret_cast<float*>(cs + (size_t)a.numCodeSlots * SX);
+  for (unsigned i = tid; i < F; i += TILE) fm[i] = a.featureMeta[i];
+  const int* __restrict__ prog = a.prog;
+  const float* __restrict__ tab = a.tab;
+  const unsigned char* __restrict__ lut = a.lut;
+  const int* __restrict__ brk = a.breaks;
+  const bool marginal = a.marginal != 0;
+
+  const unsigned long long ntiles = (n + TILE - 1) / TILE;
+  for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const unsigned long long base = tile * TILE;
+    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : TILE;
+    __syncthreads();
+    {
+      const in_t* __restrict__ src = in + base * F;
+      const unsigned total = rows * F;
+      unsigned r = tid / F, c = tid - r * F;          // element e = tid + i*TILE -> (row, column)
+      const unsigned dr = TILE / F, dc = TILE - dr * F;
+      for (unsigned e = tid; e < TILE * F; e += TILE) {
+        const int4 m = fm[c];
+        const bool live = e < total;
+        in_t raw = 0;
+        if (live) raw = src[e];
+        if (m.w >= 0) xs[m.w * SX + r] = (float)raw;
+        if (m.z >= 0) {
+          const unsigned rr = (unsigned)toIntSat<in_t>(raw) - (unsigned)m.x;
+          int code = rr < (unsigned)m.y ? (int)rr + 2 : 1;
+          if (IsFloat<in_t>::value && raw != raw) code = 0;
+          cs[m.z * SX + r] = live ? code : 1;
+        }
+        r += dr; c += dc;
+        if (c >= F) { c -= F; r += 1; }
+      }
+    }
+    __syncthreads();
+    const float* xcol = xs + tid;
+    const int* ccol = cs + tid;
+    float* v = vals + tid;
+    int pc = 0;
+    for (;;) {
+      const int op = __ldg(prog + pc);
+      if (op == OP_END) {
+        if (tid < rows) out[base + tid] = v[__ldg(prog + pc + 1) * TILE] * 0x1.62e43p-1f;
+        break;
+      }
+      const int dst = __ldg(prog + pc + 1);
+      float r;
+      switch (op) {
+        case OP_GAUSS: {
+          const float x = xcol[__ldg(prog + pc + 2) * SX];
+          const float d = x - __int_as_float(__ldg(prog + pc + 3));
+          r = fmaf(d * d, __int_as_float(__ldg(prog + pc + 4)), __int_as_float(__ldg(prog + pc + 5)));
+          if (marginal && d != d) r = 0.0f;
+          pc += 6;
+          break;
+        }
+        case OP_TABLE: {
+          int code = ccol[__ldg(prog + pc + 2) * SX];
+          const int lo = __ldg(prog + pc + 3);
+          if (lo >= 0) code = __ldg(lut + lo + code);
+          r = __ldg(tab + __ldg(prog + pc + 4) + code);
+          pc += 5;
+          break;
+        }
+        case OP_HISTG: {
+          const float x = xcol[__ldg(prog + pc + 2) * SX];
+          const int* b = brk + __ldg(prog + pc + 3);
+          const int cnt = __ldg(prog + pc + 4);
+          const int xi = __float2int_rz(x);
+          int idx = cnt;
+          if (xi >= __ldg(b) && xi < __ldg(b + cnt)) {
+            idx = 0;
+            for (int i = 1; i < cnt; ++i) idx += (xi >= __ldg(b + i));
+          }
+          if (x != x) idx = cnt + 1;
+          r = __ldg(tab + __ldg(prog + pc + 5) + idx);
+          pc += 6;
+          break;
+        }
+        case OP_PROD: {
+          const int k = __ldg(prog + pc + 2);
+          const int* s = prog + pc + 3;
+          float a0 = 0.0f, a1 = 0.0f;
+          int i = 0;
+          for (; i + 1 < k; i += 2) {
+            a0 += v[__ldg(s + i) * TILE];
+            a1 += v[__ldg(s + i + 1) * TILE];
+          }
+          if (i < k) a0 += v[__ldg(s + i) * TILE];
+          r = a0 + a1;
+          pc += 3 + k;
+          break;
+        }
+        default: {  // OP_SUM
+          const int k = __ldg(prog + pc + 2);
+          const int* s = prog + pc + 3;
+          float m = __int_as_float(0xff800000);
+          for (int i = 0; i < k; ++i) m = fmaxf(m, v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)));
+          const float mm = (m == __int_as_float(0xff800000)) ? 0.0f : m;
+          float acc0 = 0.0f, acc1 = 0.0f;
+          int i = 0;
+          for (; i + 1 < k; i += 2) {
+            acc0 += ex2(v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
+            acc1 += ex2(v[__ldg(s + 2 * i + 2) * TILE] + __int_as_float(__ldg(s + 2 * i + 3)) - mm);
+          }
+          if (i < k) acc0 += ex2(v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
+          r = m + lg2(acc0 + acc1);
+          pc += 3 + 2 * k;
+          break;
+        }
+      }
+      v[dst * TILE] = r;
+    }
+  }
+}
+
+template <typename in_t>
+cudaError_t launchT(const InterpArgs& a, const void* in, float* out, size_t n, int grid, int tile, size_t smem,
+                    cudaStream_t stream) {
+  if (smem > 48 * 1024) {  // per device and per instantiation; cheap enough to repeat
+    cudaError_t e = cudaFuncSetAttribute(interpKernel<in_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  interpKernel<in_t><<<grid, tile, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t interpSmemBytes(const InterpArgs& a, int tile) {
+  size_t sx = (size_t)tile + 1;
+  return (size_t)a.numFeatures * 16 + (size_t)a.numValueSlots * sx * 4 + (size_t)a.numCodeSlots * sx * 4 +
+         (size_t)a.numSlots * tile * 4;
+}
+
+cudaError_t interpOccupancy(int inKindCode, int tile, size_t smem, int* blocksPerSM) {
+  // all instantiations have the same resource usage up to the staging conversion; query the float one
+  (void)inKindCode;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(interpKernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, interpKernel<float>, tile, smem);
+}
+
+cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
+                         size_t smem, cudaStream_t stream) {
+  switch (dtypeCode) {
+    case DT_U8: return launchT<uint8_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_I8: return launchT<int8_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_U16: return launchT<uint16_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_I16: return launchT<int16_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_U32: return launchT<uint32_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_I32: return launchT<int32_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_U64: return launchT<uint64_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_I64: return launchT<int64_t>(a, in, out, n, grid, tile, smem, stream);
+    case DT_F32: return launchT<float>(a, in, out, n, grid, tile, smem, stream);
+    case DT_F64: return launchT<double>(a, in, out, n, grid, tile, smem, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace spnb

@@ -1,0 +1,32 @@
+// Launch interface of the interpreter kernel (interp.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "plan.h"
+
+namespace spnb {
+
+// input element types, in the order the C-ABI documents them
+enum DTypeCode : int { DT_U8 = 0, DT_I8, DT_U16, DT_I16, DT_U32, DT_I32, DT_U64, DT_I64, DT_F32, DT_F64 };
+
+struct InterpArgs {
+  const int* prog;              // device: op stream
+  const float* tab;             // device: leaf tables (log2 domain)
+  const unsigned char* lut;     // device: code -> bucket byte tables
+  const int* breaks;            // device: breaks of the generic histogram groups
+  const int4* featureMeta;      // device: per feature (lo, domain, codeSlot, valueSlot)
+  int numFeatures;
+  int numValueSlots;
+  int numCodeSlots;
+  int numSlots;
+  int marginal;
+};
+
+size_t interpSmemBytes(const InterpArgs& a, int tile);
+cudaError_t interpOccupancy(int dtypeCode, int tile, size_t smem, int* blocksPerSM);
+cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
+                         size_t smem, cudaStream_t stream);
+
+}  // namespace spnb
