@@ -25,7 +25,7 @@ typedef struct spnb_plan spnb_plan;
  * numResults, bytesPerResult, dtype). */
 typedef struct spnb_kernel_info {
   char kernel_name[256];
-  uint32_t query_type;        /* 0 = joint probability (common/include/Kernel.h:20) */
+  uint32_t query_type;        /* 1 = joint probability (common/include/Kernel.h:20) */
   uint32_t target;            /* 2 = CUDA (common/include/Kernel.h:22) */
   uint32_t batch_size;
   uint32_t num_features;
@@ -107,6 +107,12 @@ int spnb_launch_config(spnb_plan* plan, int device, int* grid, int* block, size_
 float spnb_last_kernel_ms(const spnb_plan* plan);
 
 void spnb_plan_free(spnb_plan* plan);
+
+/* Measured instruction rates of the current CUDA device, the compute denominators of the roofline:
+ * kind 0 = FP32 fused multiply-adds per second, 1 = ex2.approx per second, 2 = lg2.approx per second,
+ * 3 = FP64 fused multiply-adds per second.  No counterpart in the reference (it has no measurement
+ * code for the GPU path). */
+int spnb_measure_peak(int kind, double* ops_per_second);
 
 /* Number of CUDA devices visible (0 if there is no driver). Backs SPNCompiler.isTargetSupported("CUDA")
  * (compiler/src/Driver.cpp:47-59). */

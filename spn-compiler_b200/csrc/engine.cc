@@ -189,7 +189,14 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   const int64_t size = plan.stats.nodes + plan.stats.sumEdges + plan.stats.productEdges;
   if (opt.kernelMode == "unrolled") strat = kUnrolled;
   else if (opt.kernelMode == "interp") strat = kInterpreter;
-  else strat = size <= opt.unrollLimit ? kUnrolled : kInterpreter;
+  else {
+    // very wide sums unroll into code the JIT takes minutes to digest; the interpreter's inner
+    // loop handles them well
+    int64_t maxFanIn = 0;
+    for (size_t v = 0; v < plan.dag.size(); ++v)
+      if (plan.dag.kind[v] == kSum) maxFanIn = std::max<int64_t>(maxFanIn, plan.dag.childPtr[v + 1] - plan.dag.childPtr[v]);
+    strat = (size <= opt.unrollLimit && (maxFanIn <= 64 || !opt.logSpace)) ? kUnrolled : kInterpreter;
+  }
   if (strat == kInterpreter && !opt.logSpace)
     fail("The interpreter kernel evaluates in log space only; pass use-log-space=true for a DAG of this size");
 
@@ -388,6 +395,7 @@ Engine::DeviceState& Engine::state(int device) {
     st->ia.lut = (const unsigned char*)st->dLut;
     st->ia.breaks = st->dBreaks;
     st->ia.featureMeta = st->dMeta;
+    st->ia.progLen = (int)p.prog.size();
     st->ia.numFeatures = (int)p.features.size();
     st->ia.numValueSlots = p.numValueSlots;
     st->ia.numCodeSlots = p.numCodeSlots;

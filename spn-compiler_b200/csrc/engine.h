@@ -17,7 +17,7 @@ namespace spnb {
 
 struct KernelMeta {
   std::string kernelName;
-  uint32_t queryType = 0, target = 2, batchSize = 1, numFeatures = 0, bytesPerFeature = 0, numResults = 1,
+  uint32_t queryType = 1, target = 2, batchSize = 1, numFeatures = 0, bytesPerFeature = 0, numResults = 1,
            bytesPerResult = 4;
   std::string dtype = "float32";
 };

@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
     const int* ccol = cs + tid;
     float* v = vals + tid;
     int pc = 0;
-    for (;;) {
+    // the walk is bounded by the program length: a corrupt stream ends the tile instead of spinning
+    while (pc < a.progLen) {
       const int op = __ldg(prog + pc);
       if (op == OP_END) {
         if (tid < rows) out[base + tid] = v[__ldg(prog + pc + 1) * TILE] * 0x1.62e43p-1f;
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           break;
         }
         case OP_PROD: {
-          const int k = __ldg(prog + pc + 2);
+          const int k = min(__ldg(prog + pc + 2), a.progLen - pc);
           const int* s = prog + pc + 3;
           float a0 = 0.0f, a1 = 0.0f;
           int i = 0;
@@ -151,8 +152,8 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           pc += 3 + k;
           break;
         }
-        default: {  // OP_SUM
-          const int k = __ldg(prog + pc + 2);
+        case OP_SUM: {
+          const int k = min(__ldg(prog + pc + 2), (a.progLen - pc) / 2);
           const int* s = prog + pc + 3;
           float m = __int_as_float(0xff800000);
           for (int i = 0; i < k; ++i) m = fmaxf(m, v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)));
@@ -168,6 +169,9 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           pc += 3 + 2 * k;
           break;
         }
+        default:  // unknown opcode: stop walking
+          pc = a.progLen;
+          continue;
       }
       v[dst * TILE] = r;
     }

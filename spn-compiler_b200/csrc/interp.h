@@ -17,6 +17,7 @@ struct InterpArgs {
   const unsigned char* lut;     // device: code -> bucket byte tables
   const int* breaks;            // device: breaks of the generic histogram groups
   const int4* featureMeta;      // device: per feature (lo, domain, codeSlot, valueSlot)
+  int progLen;                  // number of int32 words in prog
   int numFeatures;
   int numValueSlots;
   int numCodeSlots;

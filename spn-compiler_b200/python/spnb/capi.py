@@ -41,6 +41,7 @@ def _load():
                                               ctypes.POINTER(sz)]),
         "spnb_last_kernel_ms": (ctypes.c_float, [vp]),
         "spnb_plan_free": (None, [vp]),
+        "spnb_measure_peak": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
         "spnb_device_count": (ctypes.c_int, []),
         "spnb_last_error": (cp, []),
         "spnb_version": (cp, []),
@@ -54,7 +55,7 @@ def _load():
 lib = _load()
 EXPORTS = ["spnb_compile", "spnb_plan_load", "spnb_plan_info", "spnb_plan_stats_json", "spnb_plan_source",
            "spnb_execute_host", "spnb_execute_device", "spnb_execute_sharded", "spnb_set_device",
-           "spnb_launch_config", "spnb_last_kernel_ms", "spnb_plan_free", "spnb_device_count", "spnb_last_error",
+           "spnb_launch_config", "spnb_last_kernel_ms", "spnb_plan_free", "spnb_measure_peak", "spnb_device_count", "spnb_last_error",
            "spnb_version"]
 
 
@@ -149,3 +150,10 @@ class Plan:
 
 def device_count():
     return int(lib.spnb_device_count())
+
+
+def measure_peak(kind):
+    """Instruction rate of the current device: 'fp32', 'ex2', 'lg2' or 'fp64' -> operations per second."""
+    v = ctypes.c_double(0.0)
+    _check(lib.spnb_measure_peak({"fp32": 0, "ex2": 1, "lg2": 2, "fp64": 3}[kind], ctypes.byref(v)))
+    return v.value

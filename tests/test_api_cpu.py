@@ -1,0 +1,152 @@
+"""Host-side logic that needs no GPU: C-ABI exports, option handling, the xspn writer/reader pair,
+planner statistics, the pybind module and the CUDACompiler front."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from tests.util_models import small_configs, write_query
+from xspn.serialization.binary.BinarySerialization import BinarySerializer
+from xspn.structure.Model import SPNModel
+from xspn.structure.Nodes import Categorical, Gaussian, Histogram, Product, Sum
+from xspn.structure.Query import JointProbability
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from spnb import capi
+    header = open(os.path.join(ROOT, "include", "spnb.h")).read()
+    declared = set(re.findall(r"\b(spnb_[a-z_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), name
+    assert declared == set(capi.EXPORTS)
+
+
+def test_no_gpu_means_a_loud_error_not_a_fallback(tmp_path):
+    from spnb import capi
+    if capi.device_count() > 0:
+        pytest.skip("a GPU is present")
+    name, spn, inputs, log_space, marginal = small_configs()[2]
+    q = write_query(spn, marginal, directory=str(tmp_path))
+    plan_path, info = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true"})
+    plan = capi.Plan(plan_path)
+    with pytest.raises(capi.SpnbError, match="no CPU fallback"):
+        plan.execute_host(inputs(8))
+
+
+def test_option_handling(tmp_path):
+    from spnb import capi
+    name, spn, inputs, log_space, marginal = small_configs()[0]
+    q = write_query(spn, False, directory=str(tmp_path))
+    with pytest.raises(capi.SpnbError, match="Unknown compile option"):
+        capi.compile_query(q, {"target": "CUDA", "no-such-option": "1"})
+    with pytest.raises(capi.SpnbError, match="target"):
+        capi.compile_query(q, {"use-log-space": "true"})
+    with pytest.raises(capi.SpnbError, match="CPU"):
+        capi.compile_query(q, {"target": "CPU"})
+    # every key the reference's Python layer may pass is accepted
+    opts = {"target": "CUDA", "use-log-space": "true", "gpu-shared-mem": "false", "dump-ir": "false",
+            "search-paths": "/tmp", "maxTaskSize": "10", "optLevel": "3", "cpu-vectorize": "false",
+            "vector-library": "None", "use-shuffle": "false", "delete-temps": "true", "opt-repr": "false",
+            "collect-graph-stats": "true", "graph-stats-file": str(tmp_path / "stats.json")}
+    path, info = capi.compile_query(q, opts)
+    assert os.path.isfile(path) and os.path.isfile(tmp_path / "stats.json")
+    assert info.dtype == b"float32" and info.bytes_per_result == 4 and info.query_type == 1 and info.target == 2
+    path, info = capi.compile_query(q, {"target": "CUDA"})  # reference default: linear space, f64 result
+    assert info.dtype == b"float64" and info.bytes_per_result == 8
+    # marginal support needs a floating feature type (int32 inputs here)
+    qm = write_query(spn, True, directory=str(tmp_path))
+    with pytest.raises(capi.SpnbError, match="floating-point to support marginal"):
+        capi.compile_query(qm, {"target": "CUDA"})
+
+
+def test_model_header_is_rejected_like_the_reference(golden_dir):
+    from spnb import capi
+    with pytest.raises(capi.SpnbError, match="Cannot compile raw models"):
+        capi.compile_query(os.path.join(golden_dir, "nltcs.bin"), {"target": "CUDA"})
+
+
+def test_planner_statistics_and_strategies(tmp_path, golden_dir):
+    from spnb import capi
+    path, info = capi.compile_query(os.path.join(golden_dir, "NIPS5.bin"), {"target": "CUDA", "use-log-space": "true"})
+    st = capi.Plan(path).stats
+    assert (st["histogram"], st["products"], st["sums"]) == (10, 2, 1) and st["strategy"] == "unrolled"
+    assert st["ops_sfu"] == 3 and st["bytes_per_sample"] == 5 * 4 + 4
+    assert info.kernel_name == b"spn_kernel" and info.num_features == 5 and info.bytes_per_feature == 4
+    path, _ = capi.compile_query(os.path.join(golden_dir, "speaker_FADG0.bin"),
+                                 {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "interp"})
+    st = capi.Plan(path).stats
+    assert st["strategy"] == "interpreter" and st["gaussian"] == 1326 and st["sum_edges"] == 51
+
+
+def test_corrupt_files_fail_cleanly(tmp_path, golden_dir):
+    from spnb import capi
+    data = open(os.path.join(golden_dir, "NIPS5.bin"), "rb").read()
+    for cut in (0, 7, 8, 40, len(data) // 2, len(data) - 8):
+        p = tmp_path / ("cut%d.bin" % cut)
+        p.write_bytes(data[:cut])
+        with pytest.raises(capi.SpnbError):
+            capi.compile_query(str(p), {"target": "CUDA"})
+    rng = np.random.default_rng(0)
+    for trial in range(30):
+        b = bytearray(data)
+        for pos in rng.integers(8, len(b), size=6):
+            b[pos] ^= 0xFF
+        p = tmp_path / ("flip%d.bin" % trial)
+        p.write_bytes(bytes(b))
+        try:
+            capi.compile_query(str(p), {"target": "CUDA", "use-log-space": "true"})
+        except capi.SpnbError:
+            pass  # an error message is fine, a crash is not
+
+
+def _toy_spn():
+    g1, g2 = Gaussian(0.5, 1.0, scope=0), Gaussian(0.25, 0.1, scope=1)
+    c1, h1 = Categorical([0.35, 0.55, 0.1], scope=2), Histogram([0, 2, 4], [0.25, 0.75], [1, 3], scope=3)
+    g3, g4 = Gaussian(-0.5, 2.0, scope=0), Gaussian(1.25, 0.7, scope=1)
+    c2, h2 = Categorical([0.2, 0.3, 0.5], scope=2), Histogram([0, 1, 4], [0.4, 0.2], [0.5, 2], scope=3)
+    return Sum([0.3, 0.5, 0.2], [Product([g1, g2, c1, h1]), Product([g3, g4, c2, h2]), Product([g1, g4, c2, h1])])
+
+
+def test_writer_output_is_read_back_by_both_readers(tmp_path):
+    from spnb import capi
+    q = JointProbability(SPNModel(_toy_spn(), "float32", "toy"), batchSize=64, supportMarginal=True)
+    path = str(tmp_path / "toy.bin")
+    BinarySerializer(path).serialize_to_file(q)
+    m = oracle.load_model(path)
+    assert (m.name, m.feature_type, m.num_features, m.support_marginal) == ("toy", "float32", 4, True)
+    plan_path, info = capi.compile_query(path, {"target": "CUDA", "use-log-space": "true"})
+    st = capi.Plan(plan_path).stats
+    # g1, g4, c2 and h1 are shared by two products and must be merged, not duplicated
+    assert st["nodes"] == 12 and st["gaussian"] == 4 and st["categorical"] == 2 and st["histogram"] == 2
+    assert info.kernel_name == b"toy" and info.batch_size == 64
+
+
+def test_pybind_module_and_cuda_compiler_front(tmp_path):
+    import spnc.spncpy as spncpy
+    from spnc.gpu import CUDACompiler
+    k = spncpy.Kernel("/tmp/x.plan", "name", 1, 2, 64, 5, 4, 1, 4, "float32")
+    assert k.fileName() == "/tmp/x.plan" and k.kernelName() == "name"
+    assert spncpy.SPNCompiler.isTargetSupported("CPU") is False
+    assert spncpy.SPNCompiler.getHostArchitecture()
+    comp = CUDACompiler(computeInLogSpace=True, spnb_kernel="auto") if False else CUDACompiler()
+    kernel = comp.compile_ll(_toy_spn(), inputDataType="float32")
+    assert os.path.isfile(kernel.fileName()) and kernel.kernelName() == "spn_gpu"
+    with pytest.raises(RuntimeError, match="two-dimensional"):
+        comp.execute(kernel, np.zeros(4, np.float32))
+    with pytest.raises(RuntimeError, match="numpy array"):
+        comp.execute(kernel, [[0.0] * 4])
+    with pytest.raises(RuntimeError, match="element size"):
+        comp.execute(kernel, np.zeros((2, 4), np.float64))
+    if not CUDACompiler.isAvailable():
+        with pytest.raises(RuntimeError, match="RUNTIME ERROR"):
+            comp.execute(kernel, np.zeros((2, 4), np.float32))
+    with pytest.raises(RuntimeError, match="COMPILATION ERROR"):
+        CUDACompiler(bogus="1").compile_ll(_toy_spn(), inputDataType="float32")
+    os.remove(kernel.fileName())

@@ -56,6 +56,8 @@ def test_reference_goldens_on_gpu(capi, golden_dir, tmp_path):
             q = str(tmp_path / (name + "_query.bin"))
             _rewrap_as_query(d, q)
         for log_space, tol in ((True, REL_TOL_F32), (False, REL_TOL_F64)):
+            if name == "nltcs" and not log_space:
+                continue  # sums with up to 640 addends: linear-space code is unrolled only, minutes of JIT
             plan_path, _ = capi.compile_query(q, _opts(log_space))
             plan = capi.Plan(plan_path)
             got = plan.execute_host(x)
