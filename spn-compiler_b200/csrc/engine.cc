@@ -287,6 +287,7 @@ struct Engine::DeviceState {
   void* dOut = nullptr;
   void* hOut = nullptr;
   size_t outBytes = 0;
+  std::mutex hostMu;  // one host-path call at a time per device: the staging buffers are shared
 
   ~DeviceState() {
     cudaSetDevice(device);
@@ -459,6 +460,7 @@ void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, fl
   if (kernelMs) *kernelMs = 0.f;
   if (n == 0) return;
   DeviceState& st = state(device);
+  std::lock_guard<std::mutex> hostLock(st.hostMu);
   CUDA_OK(cudaSetDevice(device));
   const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature;
   const size_t resBytes = meta_.bytesPerResult;
