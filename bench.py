@@ -183,6 +183,7 @@ def main():
     import torch
     import torch.distributed as dist
     from spnb import capi  # fails loudly if libspnb.so is missing
+    from spnb.shard import dataset_mean, max_over_ranks
 
     if capi.device_count() == 0:
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
@@ -234,18 +235,13 @@ def main():
     clocks = sampler.stop()
     if world > 1:
         dist.barrier()
-        t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+        ms_total = max_over_ranks(ms_total)
     ms_step = ms_total / args.steps
     value = n * world / (ms_step * 1e-3)
 
     # optional dataset-mean log-likelihood: the only place a collective is used
-    mean_ll = dout.double().mean()
-    if world > 1:
-        dist.all_reduce(mean_ll, op=dist.ReduceOp.SUM)
-        mean_ll = mean_ll / world
-    mean_ll = float(mean_ll.item())
+    mean_ll = float(dout.double().sum().item())
+    mean_ll = dataset_mean(mean_ll, n) if world > 1 else mean_ll / n
 
     # end to end through the host-pointer entry point, pinned host buffers, copies inside the timed region
     pin_x = torch.from_numpy(host_x).pin_memory()
@@ -260,9 +256,7 @@ def main():
     e2e_s = (time.perf_counter() - t0) / args.e2e_steps
     e2e_kernel_ms = plan.last_kernel_ms
     if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+        e2e_s = max_over_ranks(e2e_s)
     same = bool(torch.equal(pin_out.cuda(), dout))
 
     if rank == 0:
