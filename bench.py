@@ -277,6 +277,7 @@ def main():
         ex2 = capi.measure_peak("ex2")
         lg2 = capi.measure_peak("lg2")
         fp64 = capi.measure_peak("fp64")
+        fp32x2 = capi.measure_peak("fp32x2")
         if cfg["log_space"]:
             sfu_rate = min(ex2, lg2)
             t_fp32 = stats["ops_fp32"] * n / fp32
@@ -306,7 +307,7 @@ def main():
                          "note": "algorithmic bytes = %d B/sample x %d samples per launch; this workload is compute-bound, see roofline_compute" % (stats["bytes_per_sample"], n)},
             "roofline_compute": {"bound": bound, "ops_per_sample": ops, "achieved": ops * n / (ms_step * 1e-3),
                                  "peak": peak_ops, "unit": "op/s", "frac": (ops * n / peak_ops) / (ms_step * 1e-3),
-                                 "measured_rates": {"fp32_fma": fp32, "ex2": ex2, "lg2": lg2, "fp64_fma": fp64},
+                                 "measured_rates": {"fp32_fma": fp32, "fp32_fma_packed_pairs": fp32x2, "ex2": ex2, "lg2": lg2, "fp64_fma": fp64},
                                  "per_config_roofline_frac": t_roof / (ms_step * 1e-3), "t_roof_ms": t_roof * 1e3},
             "mean_ll": mean_ll,
         }

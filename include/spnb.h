@@ -110,7 +110,8 @@ void spnb_plan_free(spnb_plan* plan);
 
 /* Measured instruction rates of the current CUDA device, the compute denominators of the roofline:
  * kind 0 = FP32 fused multiply-adds per second, 1 = ex2.approx per second, 2 = lg2.approx per second,
- * 3 = FP64 fused multiply-adds per second.  No counterpart in the reference (it has no measurement
+ * 3 = FP64 fused multiply-adds per second, 4 = FP32 fused multiply-adds per second issued as packed pairs
+ * (fma.rn.f32x2).  No counterpart in the reference (it has no measurement
  * code for the GPU path). */
 int spnb_measure_peak(int kind, double* ops_per_second);
 

@@ -9,10 +9,12 @@
 namespace spnb {
 
 struct EmitOptions {
-  int tile = 128;          // threads per CTA = samples per tile
-  int minBlocksPerSM = 4;  // __launch_bounds__ hint
+  int tile = 0;            // threads per CTA = samples per tile (0: chosen from the shared-memory budget)
+  int minBlocksPerSM = 0;  // __launch_bounds__ hint (0: derived from the tile)
   int syncEvery = 0;       // CTA barrier every this many DAG nodes (0 = never): keeps the warps of a CTA
                            // on the same stretch of the instruction stream
+  int gaussForm = 1;       // 1: fma(d, d, c1/c2) * c2 (three instructions); 0: fma(d*d, c2, c1)
+  bool useMax3 = true;     // three-input max.f32 (needs a JIT that knows PTX ISA 8.8)
   int smemTableLimit = 64 * 1024;  // leaf tables larger than this stay in global memory
 };
 

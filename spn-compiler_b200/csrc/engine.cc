@@ -169,6 +169,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-sync-every") o.syncEvery = std::atoi(v.c_str());
     else if (k == "spnb-unroll-limit") o.unrollLimit = std::atoi(v.c_str());
     else if (k == "spnb-max-registers") o.maxRegisters = std::atoi(v.c_str());
+    else if (k == "spnb-gauss-form") o.gaussForm = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -208,6 +209,8 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     if (opt.tile) eo.tile = opt.tile;
     if (opt.minBlocks) eo.minBlocksPerSM = opt.minBlocks;
     eo.syncEvery = opt.syncEvery;
+    eo.gaussForm = opt.gaussForm;
+    eo.useMax3 = jitVersion() >= 1209;
     source = emitCuda(plan, eo, &ei);
     if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
     jr = jitCompile(source, m.name, opt.optLevel, opt.maxRegisters);

@@ -36,6 +36,7 @@ struct Options {
   int syncEvery = 0;           // "spnb-sync-every"
   int unrollLimit = 20000;     // "spnb-unroll-limit": nodes + edges up to which a DAG is unrolled
   int maxRegisters = 0;        // "spnb-max-registers"
+  int gaussForm = 1;           // "spnb-gauss-form"
   std::vector<std::pair<std::string, std::string>> raw;
 };
 

@@ -46,7 +46,7 @@ template <typename T> struct IsFloat { static constexpr bool value = false; };
 template <> struct IsFloat<float> { static constexpr bool value = true; };
 template <> struct IsFloat<double> { static constexpr bool value = true; };
 
-// Shared memory: [fm int4 x F][xs float x NV*SX][cs int x NC*SX][vals float x nslots*TILE]
+// Shared memory: [fm int4 x F][xs float x NV*SX][cs u16 x NC*SX][pad to 4][vals float x nslots*TILE]
 template <typename in_t>
 __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* __restrict__ in, float* __restrict__ out,
                                                        unsigned long long n) {
@@ -57,8 +57,8 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
   const unsigned F = a.numFeatures;
   int4* fm = reinterpret_cast<int4*>(smem_raw);
   float* xs = reinterpret_cast<float*>(smem_raw + (size_t)F * 16);
-  int* cs = reinterpret_cast<int*>(xs + (size_t)a.numValueSlots * SX);
-  float* vals = reinterpret_cast<float*>(cs + (size_t)a.numCodeSlots * SX);
+  unsigned short* cs = reinterpret_cast<unsigned short*>(xs + (size_t)a.numValueSlots * SX);
+  float* vals = reinterpret_cast<float*>(smem_raw + a.valsOffset(TILE));
   for (unsigned i = tid; i < F; i += TILE) fm[i] = a.featureMeta[i];
   const int* __restrict__ prog = a.prog;
   const float* __restrict__ tab = a.tab;
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           const unsigned rr = (unsigned)toIntSat<in_t>(raw) - (unsigned)m.x;
           int code = rr < (unsigned)m.y ? (int)rr + 2 : 1;
           if (IsFloat<in_t>::value && raw != raw) code = 0;
-          cs[m.z * SX + r] = live ? code : 1;
+          cs[m.z * SX + r] = (unsigned short)(live ? code : 1);
         }
         r += dr; c += dc;
         if (c >= F) { c -= F; r += 1; }
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
     }
     __syncthreads();
     const float* xcol = xs + tid;
-    const int* ccol = cs + tid;
+    const unsigned short* ccol = cs + tid;
     float* v = vals + tid;
     int pc = 0;
     // the walk is bounded by the program length: a corrupt stream ends the tile instead of spinning
@@ -192,9 +192,7 @@ cudaError_t launchT(const InterpArgs& a, const void* in, float* out, size_t n, i
 }  // namespace
 
 size_t interpSmemBytes(const InterpArgs& a, int tile) {
-  size_t sx = (size_t)tile + 1;
-  return (size_t)a.numFeatures * 16 + (size_t)a.numValueSlots * sx * 4 + (size_t)a.numCodeSlots * sx * 4 +
-         (size_t)a.numSlots * tile * 4;
+  return a.valsOffset((unsigned)tile) + (size_t)a.numSlots * tile * 4;
 }
 
 cudaError_t interpOccupancy(int inKindCode, int tile, size_t smem, int* blocksPerSM) {

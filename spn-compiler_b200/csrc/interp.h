@@ -23,6 +23,12 @@ struct InterpArgs {
   int numCodeSlots;
   int numSlots;
   int marginal;
+  // byte offset of the value slots behind the staged inputs for a CTA of `tile` threads
+  __host__ __device__ size_t valsOffset(unsigned tile) const {
+    size_t sx = (size_t)tile + 1;
+    size_t o = (size_t)numFeatures * 16 + (size_t)numValueSlots * sx * 4 + (size_t)numCodeSlots * sx * 2;
+    return (o + 3) & ~(size_t)3;
+  }
 };
 
 size_t interpSmemBytes(const InterpArgs& a, int tile);

@@ -12,6 +12,9 @@ struct JitResult {
   int spillBytes = -1;   // spill stores + loads in bytes, -1 if not found
 };
 
+// NVRTC version as major * 100 + minor (e.g. 1209).
+int jitVersion();
+
 // Throws std::runtime_error (message contains the compiler log) on failure.
 JitResult jitCompile(const std::string& source, const std::string& name, int optLevel, int maxRegisters);
 

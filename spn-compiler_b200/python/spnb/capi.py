@@ -155,5 +155,5 @@ def device_count():
 def measure_peak(kind):
     """Instruction rate of the current device: 'fp32', 'ex2', 'lg2' or 'fp64' -> operations per second."""
     v = ctypes.c_double(0.0)
-    _check(lib.spnb_measure_peak({"fp32": 0, "ex2": 1, "lg2": 2, "fp64": 3}[kind], ctypes.byref(v)))
+    _check(lib.spnb_measure_peak({"fp32": 0, "ex2": 1, "lg2": 2, "fp64": 3, "fp32x2": 4}[kind], ctypes.byref(v)))
     return v.value
