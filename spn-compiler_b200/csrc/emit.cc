@@ -70,7 +70,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   if (TILE <= 0) {
     const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * 2 + 4;
     size_t fixed = (size_t)d.numFeatures * 16 + 64;
-    if (tabEntries * realBytes <= (size_t)opt.smemTableLimit) fixed += tabEntries * realBytes;
+    fixed += std::min(tabEntries * realBytes, (size_t)opt.smemTableLimit) + 16;
     if (p.lut.size() <= (size_t)opt.smemTableLimit) fixed += p.lut.size();
     const size_t budget = 200 * 1024;
     TILE = 1024;
@@ -80,7 +80,13 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     minBlocks = std::max(1, 1024 / TILE);
   }
   const int SX = TILE + 1;
-  const bool tabSmem = tabEntries > 0 && tabEntries * realBytes <= (size_t)opt.smemTableLimit;
+  // Leaf tables are always read from shared memory.  Tables larger than the window are streamed
+  // through it: leaves appear in the body in table order, so at the points where the next leaf's
+  // table lies beyond the window the CTA reloads the window from global memory between two barriers.
+  const bool tabSmem = tabEntries > 0;
+  const size_t tabBytes = tabEntries * realBytes;
+  const bool streamed = tabBytes > (size_t)opt.smemTableLimit;
+  const size_t winBytes = streamed ? ((size_t)opt.smemTableLimit & ~size_t(15)) : ((tabBytes + 15) & ~size_t(15));
   const bool floatIn = p.ftype.isFloat();
   const double LOG2E = 1.4426950408889634074;
   const int NV = p.numValueSlots, NC = p.numCodeSlots;
@@ -97,8 +103,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const size_t offFm = 0;
   const size_t offXs = identity ? 0 : (size_t)F * 16;
   const size_t offCs = offXs + (size_t)NV * SX * realBytes;
-  const size_t offTab = (offCs + (size_t)NC * SX * 2 + 7) & ~size_t(7);
-  const size_t offLut = offTab + (tabSmem ? tabEntries * realBytes : 0);
+  const size_t offTab = (offCs + (size_t)NC * SX * 2 + 15) & ~size_t(15);
+  const size_t offLut = offTab + (tabSmem ? winBytes : 0);
   const size_t offNan = (offLut + (lutSmem ? p.lut.size() : 0) + 3) & ~size_t(3);
   const size_t smemTotal = offNan + (twoBodies ? (size_t)TILE * 4 : 0);
 
@@ -150,12 +156,25 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   auto readCode = [&](const std::string& dst, int slot, long long node) {
     return ldsStmt("int", "ld.shared.u16", "r", dst, "cs_t", 2ll * slot * SX, node);
   };
+  long long winBase = 0;  // first table entry held by the window at the current point of the body
   auto readTab = [&](const std::string& dst, long long off, const std::string& idx, long long node) {
-    if (tabSmem) return ldsStmt("real_t", ldReal, cReal, dst, "(tab_s + " + std::to_string(rb) + "u * (unsigned)" + idx + ")", (long long)rb * off, node);
-    std::ostringstream e;  // read-only global path, same asm form (64-bit address operand)
-    e << "  real_t " << dst << "; asm(\"" << (lg ? "ld.global.nc.f32" : "ld.global.nc.f64") << " %0, [%1+" << (long long)rb * off
-      << "]; // " << node << "\" : \"=" << cReal << "\"(" << dst << ") : \"l\"(tab_g + " << idx << "));\n";
-    return e.str();
+    std::string st = ldsStmt("real_t", ldReal, cReal, dst, "(tab_s + " + std::to_string(rb) + "u * (unsigned)" + idx + ")",
+                             (long long)rb * (off - winBase), node);
+    // a streamed window changes under the body: its reads must stay between the surrounding barriers
+    if (streamed) st.replace(st.find("asm("), 4, "asm volatile(");
+    return st;
+  };
+  auto tableEntriesOf = [&](size_t v) -> long long {
+    const IndexGroup& G = p.groups[d.group[v]];
+    return G.mode == kDirect ? (long long)p.features[G.feature].domain + 2 : (long long)G.count + 2;
+  };
+  auto swapWindow = [&](std::ostringstream& out, long long firstEntry) {
+    const long long align = 16 / rb;
+    winBase = firstEntry / align * align;
+    out << "  __syncthreads();\n";
+    out << "  { const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(tab_g) + " << winBase * rb << "ll);\n";
+    out << "    for (unsigned i = tid; i < " << winBytes / 16 << "u; i += TILE) win[i] = __ldg(src + i); }\n";
+    out << "  __syncthreads();\n";
   };
   auto readLut = [&](const std::string& dst, long long off, const std::string& idx, long long node) {
     if (lutSmem) return ldsStmt("int", "ld.shared.u8", "r", dst, "(lut_s + (unsigned)" + idx + ")", off, node);
@@ -213,8 +232,10 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // barrier that follows the staging of a tile) ------------------------------------------------------
   auto emitBody = [&](const char* fname, bool nanAware) {
   o << "static __device__ __noinline__ out_t " << fname << "(const unsigned xs_s, const unsigned cs_s, const unsigned tab_s, "
-       "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, const unsigned tid)\n{\n";
+       "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, uint4* __restrict__ win, const unsigned tid)\n{\n";
   o << "  const unsigned xs_t = xs_s + " << rb << "u * tid;\n  const unsigned cs_t = cs_s + 2u * tid;\n";
+  winBase = 0;
+  if (streamed) swapWindow(o, 0);
   std::vector<std::string> terms;
   for (size_t v = 0; v < n; ++v) {
     if (opt.syncEvery > 0 && v > 0 && v % (size_t)opt.syncEvery == 0) o << "  __syncthreads();\n";
@@ -249,6 +270,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       }
       case kCategorical:
       case kHistogram:
+        if (streamed && (p.tabOffset[v] + tableEntriesOf(v) - winBase) * rb > (long long)winBytes) swapWindow(o, p.tabOffset[v]);
         emitLeafLookup(o, v, name);
         break;
       case kProduct: {
@@ -320,9 +342,10 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "  int4* fm = reinterpret_cast<int4*>(smem_raw + " << offFm << ");\n";
     o << "  for (unsigned i = tid; i < NF; i += TILE) fm[i] = make_int4(FM[4 * i], FM[4 * i + 1], FM[4 * i + 2], FM[4 * i + 3]);\n";
   }
+  o << "  uint4* win = reinterpret_cast<uint4*>(smem_raw + " << offTab << ");\n";
   if (tabSmem) {
-    o << "  { real_t* tab = reinterpret_cast<real_t*>(smem_raw + " << offTab << ");\n";
-    o << "    for (unsigned i = tid; i < NTAB; i += TILE) tab[i] = tab_g[i];\n    tab_s = (unsigned)__cvta_generic_to_shared(tab); }\n";
+    o << "  tab_s = (unsigned)__cvta_generic_to_shared(win);\n";
+    if (!streamed) o << "  for (unsigned i = tid; i < NTAB; i += TILE) reinterpret_cast<real_t*>(win)[i] = tab_g[i];\n";
   }
   if (lutSmem) {
     o << "  { unsigned char* lut = smem_raw + " << offLut << ";\n";
@@ -364,10 +387,10 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   if (twoBodies) {
     o << "    const int mynan = nanrow[tid];\n    nanrow[tid] = 0;\n";
     // the choice is uniform over the CTA, so barriers inside the bodies stay legal
-    o << "    const out_t res = __syncthreads_or(mynan) ? spnb_body_nan(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, tid)\n"
-         "                                              : spnb_body(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, tid);\n";
+    o << "    const out_t res = __syncthreads_or(mynan) ? spnb_body_nan(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, tid)\n"
+         "                                              : spnb_body(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, tid);\n";
   } else {
-    o << "    const out_t res = spnb_body(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, tid);\n";
+    o << "    const out_t res = spnb_body(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, tid);\n";
   }
   o << "    if (tid < rows) out[base + tid] = res;\n";
   o << "  }\n}\n";

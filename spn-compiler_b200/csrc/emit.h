@@ -15,7 +15,7 @@ struct EmitOptions {
                            // on the same stretch of the instruction stream
   int gaussForm = 1;       // 1: fma(d, d, c1/c2) * c2 (three instructions); 0: fma(d*d, c2, c1)
   bool useMax3 = true;     // three-input max.f32 (needs a JIT that knows PTX ISA 8.8)
-  int smemTableLimit = 64 * 1024;  // leaf tables larger than this stay in global memory
+  int smemTableLimit = 64 * 1024;  // shared-memory window for leaf tables; larger tables are streamed through it
 };
 
 struct EmitInfo {

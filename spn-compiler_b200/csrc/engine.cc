@@ -170,6 +170,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-unroll-limit") o.unrollLimit = std::atoi(v.c_str());
     else if (k == "spnb-max-registers") o.maxRegisters = std::atoi(v.c_str());
     else if (k == "spnb-gauss-form") o.gaussForm = std::atoi(v.c_str());
+    else if (k == "spnb-table-window") o.tableWindow = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -210,6 +211,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     if (opt.minBlocks) eo.minBlocksPerSM = opt.minBlocks;
     eo.syncEvery = opt.syncEvery;
     eo.gaussForm = opt.gaussForm;
+    if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
     eo.useMax3 = jitVersion() >= 1209;
     source = emitCuda(plan, eo, &ei);
     if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
@@ -365,9 +367,11 @@ Engine::DeviceState& Engine::state(int device) {
   CUDA_OK(cudaGetDeviceProperties(&prop, device));
   st->smCount = prop.multiProcessorCount;
   const Plan& p = plan_;
+  // padded: a streamed table window may be loaded whole even when it starts near the table's end
   auto upload = [&](const void* src, size_t bytes) -> void* {
     void* d = nullptr;
-    CUDA_OK(cudaMalloc(&d, std::max<size_t>(bytes, 16)));
+    CUDA_OK(cudaMalloc(&d, bytes + (256u << 10)));
+    CUDA_OK(cudaMemset(d, 0, bytes + (256u << 10)));
     if (bytes) CUDA_OK(cudaMemcpy(d, src, bytes, cudaMemcpyHostToDevice));
     return d;
   };

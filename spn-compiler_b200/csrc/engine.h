@@ -37,6 +37,7 @@ struct Options {
   int unrollLimit = 20000;     // "spnb-unroll-limit": nodes + edges up to which a DAG is unrolled
   int maxRegisters = 0;        // "spnb-max-registers"
   int gaussForm = 1;           // "spnb-gauss-form"
+  int tableWindow = 0;         // "spnb-table-window": bytes of shared memory for leaf tables (0 = 64 KB)
   std::vector<std::pair<std::string, std::string>> raw;
 };
 

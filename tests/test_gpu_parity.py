@@ -83,6 +83,22 @@ def _rewrap_as_query(d, path):
         f.write(data)
 
 
+def test_streamed_table_window(capi, tmp_path):
+    """Leaf tables larger than the shared-memory window are reloaded piecewise inside the kernel body."""
+    for idx in (3, 4, 1):
+        name, spn, inputs, log_space, marginal = small_configs()[idx]
+        q = write_query(spn, marginal, directory=str(tmp_path))
+        plan_path, _ = capi.compile_query(q, _opts(log_space, spnb_kernel="unrolled", spnb_table_window=1024))
+        plan = capi.Plan(plan_path)
+        assert "win[i] = __ldg" in plan.source and plan.source.count("win[i] = __ldg") > 4
+        for n in (1, 1000, 70001):
+            x = inputs(n)
+            err = max_rel_err(plan.execute_host(x), oracle_eval(q, x, log_space))
+            assert err <= REL_TOL_F32, (name, n, err)
+        plan.close()
+        os.remove(plan_path)
+
+
 def test_device_pointer_entry_matches_host_entry(capi, tmp_path):
     import torch
     name, spn, inputs, log_space, marginal = small_configs()[2]
