@@ -228,16 +228,64 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   }
 
   auto V = [](int32_t i) { return "v" + std::to_string(i); };
+  // ---- chunking.  A DAG with more than chunkNodes nodes is emitted as a sequence of functions over
+  // consecutive stretches of the evaluation order (the JIT's time grows much faster than linearly with
+  // the size of one function).  A value defined in one chunk and used in a later one travels through a
+  // per-CTA scratch area in global memory, [slot][TILE] so that a warp's access is one 128-byte line;
+  // slots are reused once their last consumer has run.
+  const size_t chunkNodes = opt.chunkNodes > 0 ? (size_t)opt.chunkNodes : n;
+  const size_t nChunks = (n + chunkNodes - 1) / chunkNodes;
+  std::vector<int32_t> crossSlot(n, -1);
+  int32_t nCross = 0;
+  if (nChunks > 1) {
+    std::vector<int64_t> lastUse(n, -1);
+    std::vector<uint8_t> isCross(n, 0);
+    for (size_t v = 0; v < n; ++v)
+      for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
+        int32_t c = d.childIdx[e];
+        lastUse[c] = std::max<int64_t>(lastUse[c], (int64_t)v);
+        if ((size_t)c / chunkNodes != v / chunkNodes) isCross[c] = 1;
+      }
+    std::vector<std::vector<int32_t>> dying(n);
+    for (size_t v = 0; v < n; ++v)
+      if (isCross[v]) dying[(size_t)lastUse[v]].push_back((int32_t)v);
+    std::vector<int32_t> freeSlots;
+    for (size_t v = 0; v < n; ++v) {
+      if (isCross[v]) {
+        if (!freeSlots.empty()) { crossSlot[v] = freeSlots.back(); freeSlots.pop_back(); }
+        else crossSlot[v] = nCross++;
+      }
+      // a slot is released after its last consumer: that consumer's load precedes, in program order,
+      // every store a later definition may make to the same slot
+      for (int32_t c : dying[v]) freeSlots.push_back(crossSlot[c]);
+    }
+  }
+  const char* ldGlobal = lg ? "ld.global.f32" : "ld.global.f64";
+  const char* stGlobal = lg ? "st.global.f32" : "st.global.f64";
   // ---- the DAG body: its own non-inlined function (the asm reads above must not move across the
   // barrier that follows the staging of a tile) ------------------------------------------------------
-  auto emitBody = [&](const char* fname, bool nanAware) {
+  auto emitBody = [&](const std::string& fname, bool nanAware, size_t chunk) {
+  const size_t v0 = chunk * chunkNodes, v1 = std::min(n, v0 + chunkNodes);
   o << "static __device__ __noinline__ out_t " << fname << "(const unsigned xs_s, const unsigned cs_s, const unsigned tab_s, "
-       "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, uint4* __restrict__ win, const unsigned tid)\n{\n";
+       "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, uint4* __restrict__ win, "
+       "real_t* __restrict__ sc, const unsigned tid)\n{\n";
   o << "  const unsigned xs_t = xs_s + " << rb << "u * tid;\n  const unsigned cs_t = cs_s + 2u * tid;\n";
-  winBase = 0;
-  if (streamed) swapWindow(o, 0);
+  if (chunk == 0) {
+    winBase = 0;
+    if (streamed) swapWindow(o, 0);
+  }
+  std::vector<uint8_t> loaded(nChunks > 1 ? n : 0, 0);
   std::vector<std::string> terms;
-  for (size_t v = 0; v < n; ++v) {
+  for (size_t v = v0; v < v1; ++v) {
+    // operands defined by an earlier chunk are fetched from the scratch area on first use
+    if (nChunks > 1)
+      for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
+        const int32_t c = d.childIdx[e];
+        if ((size_t)c >= v0 || loaded[c]) continue;
+        loaded[c] = 1;
+        o << "  real_t " << V(c) << "; asm volatile(\"" << ldGlobal << " %0, [%1+" << (long long)crossSlot[c] * TILE * rb
+          << "];\" : \"=" << cReal << "\"(" << V(c) << ") : \"l\"(sc) : \"memory\");\n";
+      }
     if (opt.syncEvery > 0 && v > 0 && v % (size_t)opt.syncEvery == 0) o << "  __syncthreads();\n";
     const std::string name = V((int32_t)v);
     int64_t lo = d.childPtr[v], hi = d.childPtr[v + 1];
@@ -316,21 +364,25 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
         o << "  const float " << name << " = m" << v << " + lg2(s" << v << ");\n";
       }
     }
+    if (crossSlot[v] >= 0)
+      o << "  asm volatile(\"" << stGlobal << " [%0+" << (long long)crossSlot[v] * TILE * rb << "], %1;\" :: \"l\"(sc), \""
+        << cReal << "\"(" << name << ") : \"memory\");\n";
   }
-  if (lg) o << "  return " << V(d.root()) << " * 0x1.62e43p-1f;\n}\n";  // log2 -> ln
+  if (v1 < n) o << "  return (out_t)0;\n}\n";
+  else if (lg) o << "  return " << V(d.root()) << " * 0x1.62e43p-1f;\n}\n";  // log2 -> ln
   else o << "  return log(" << V(d.root()) << ");\n}\n";
 
   };
-  if (twoBodies) {
-    emitBody("spnb_body", false);
-    emitBody("spnb_body_nan", true);
-  } else {
-    emitBody("spnb_body", p.marginal && floatIn);
-  }
+  for (int variant = 0; variant < (twoBodies ? 2 : 1); ++variant)
+    for (size_t c = 0; c < nChunks; ++c)
+      emitBody(std::string(variant ? "spnb_body_nan" : "spnb_body") + std::to_string(c),
+               twoBodies ? variant == 1 : (p.marginal && floatIn), c);
 
   // ---- kernel: persistent CTAs, stage a tile of TILE samples, evaluate, store -------------------
   o << "extern \"C\" __global__ void __launch_bounds__(TILE, " << minBlocks << ")\n";
-  o << "spnb_kernel(const in_t* __restrict__ in, out_t* __restrict__ out, unsigned long long n, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g)\n{\n";
+  o << "spnb_kernel(const in_t* __restrict__ in, out_t* __restrict__ out, unsigned long long n, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, real_t* __restrict__ scratch)\n{\n";
+  if (nCross > 0) o << "  real_t* sc = scratch + ((size_t)blockIdx.x * " << nCross << "u * TILE + threadIdx.x);\n";
+  else o << "  real_t* sc = scratch;\n";
   o << "  extern __shared__ __align__(16) unsigned char smem_raw[];\n";
   o << "  const unsigned tid = threadIdx.x;\n";
   o << "  real_t* xs = reinterpret_cast<real_t*>(smem_raw + " << offXs << ");\n";
@@ -384,13 +436,21 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   }
   o << "    }\n";
   o << "    __syncthreads();\n";
+  auto callChain = [&](const char* prefix, const char* indent) {
+    for (size_t c = 0; c < nChunks; ++c)
+      o << indent << (c + 1 == nChunks ? "res = " : "") << prefix << c << "(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, sc, tid);\n";
+  };
+  o << "    out_t res;\n";
   if (twoBodies) {
     o << "    const int mynan = nanrow[tid];\n    nanrow[tid] = 0;\n";
     // the choice is uniform over the CTA, so barriers inside the bodies stay legal
-    o << "    const out_t res = __syncthreads_or(mynan) ? spnb_body_nan(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, tid)\n"
-         "                                              : spnb_body(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, tid);\n";
+    o << "    if (__syncthreads_or(mynan)) {\n";
+    callChain("spnb_body_nan", "      ");
+    o << "    } else {\n";
+    callChain("spnb_body", "      ");
+    o << "    }\n";
   } else {
-    o << "    const out_t res = spnb_body(xs_s, cs_s, tab_s, lut_s, tab_g, lut_g, win, tid);\n";
+    callChain("spnb_body", "    ");
   }
   o << "    if (tid < rows) out[base + tid] = res;\n";
   o << "  }\n}\n";
@@ -402,6 +462,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     info->tablesInSmem = tabSmem;
     info->tableEntries = tabEntries;
     info->dynamicSmemBytes = smemTotal;
+    info->scratchSlots = nCross;
   }
   return o.str();
 }

@@ -86,7 +86,7 @@ int dtypeCode(const FeatureType& t) {
 }
 
 // ---- plan file -----------------------------------------------------------------------------------
-const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '2'};
+const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '3'};
 
 struct Writer {
   std::vector<uint8_t> b;
@@ -116,7 +116,7 @@ std::string makeStatsJson(const Plan& p, Strategy s, const EmitInfo& ei, int reg
   o << base << ",\"log_space\":" << (p.logSpace ? "true" : "false") << ",\"strategy\":\""
     << (s == kUnrolled ? "unrolled" : "interpreter") << "\",\"tile\":" << ei.tile << ",\"registers\":" << regs
     << ",\"spill_bytes\":" << spill << ",\"smem_bytes\":" << ei.dynamicSmemBytes << ",\"interp_slots\":" << interpSlots
-    << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
+    << ",\"scratch_slots\":" << ei.scratchSlots << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
   return o.str();
 }
 
@@ -171,6 +171,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-max-registers") o.maxRegisters = std::atoi(v.c_str());
     else if (k == "spnb-gauss-form") o.gaussForm = std::atoi(v.c_str());
     else if (k == "spnb-table-window") o.tableWindow = std::atoi(v.c_str());
+    else if (k == "spnb-chunk-nodes") o.chunkNodes = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -211,6 +212,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     if (opt.minBlocks) eo.minBlocksPerSM = opt.minBlocks;
     eo.syncEvery = opt.syncEvery;
     eo.gaussForm = opt.gaussForm;
+    if (opt.chunkNodes >= 0) eo.chunkNodes = opt.chunkNodes;
     if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
     eo.useMax3 = jitVersion() >= 1209;
     source = emitCuda(plan, eo, &ei);
@@ -248,6 +250,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   w.u64((uint64_t)strat);
   w.u64((uint64_t)ei.tile);
   w.u64((uint64_t)ei.dynamicSmemBytes);
+  w.u64((uint64_t)ei.scratchSlots);
   w.u64((uint64_t)(jr.registers + 1));
   w.u64((uint64_t)(jr.spillBytes + 1));
   w.blob(xspn.data(), xspn.size());
@@ -283,6 +286,7 @@ struct Engine::DeviceState {
   int grid = 0, block = 0;
   size_t smem = 0;
   InterpArgs ia{};
+  void* dScratch = nullptr;   // per-CTA scratch of a chunked generated kernel: [grid][slots][tile] values
   // host path
   static constexpr int kBuf = 3;
   cudaStream_t streams[kBuf] = {nullptr, nullptr, nullptr};
@@ -308,6 +312,7 @@ struct Engine::DeviceState {
     if (dProg) cudaFree(dProg);
     if (dBreaks) cudaFree(dBreaks);
     if (dMeta) cudaFree(dMeta);
+    if (dScratch) cudaFree(dScratch);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -330,6 +335,7 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->strategy_ = (Strategy)r.u64();
   e->emitInfo_.tile = (int)r.u64();
   e->emitInfo_.dynamicSmemBytes = (size_t)r.u64();
+  e->emitInfo_.scratchSlots = (int)r.u64();
   int regs = (int)r.u64() - 1;
   int spill = (int)r.u64() - 1;
   std::vector<uint8_t> xspn = r.blob();
@@ -391,6 +397,10 @@ Engine::DeviceState& Engine::state(int device) {
     drv.check(drv.occupancy(&perSM, st->fn, st->block, st->smem), "cuOccupancyMaxActiveBlocksPerMultiprocessor");
     if (perSM < 1) fail("Generated kernel does not fit on one SM");
     st->grid = perSM * st->smCount;
+    if (emitInfo_.scratchSlots > 0) {
+      size_t bytes = (size_t)st->grid * emitInfo_.scratchSlots * st->block * (p.logSpace ? 4 : 8);
+      CUDA_OK(cudaMalloc(&st->dScratch, bytes));
+    }
   } else {
     std::vector<int4> meta(p.features.size());
     for (size_t f = 0; f < meta.size(); ++f)
@@ -442,7 +452,7 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
   const int grid = (int)std::min<size_t>(tiles, (size_t)st.grid);
   if (strategy_ == kUnrolled) {
     unsigned long long nn = n;
-    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut};
+    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&st.dScratch};
     Driver& drv = Driver::get();
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");

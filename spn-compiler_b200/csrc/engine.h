@@ -34,9 +34,10 @@ struct Options {
   int tile = 0;                // "spnb-tile": threads per CTA (0 = default)
   int minBlocks = 0;           // "spnb-min-blocks": __launch_bounds__ hint of the generated kernel
   int syncEvery = 0;           // "spnb-sync-every"
-  int unrollLimit = 20000;     // "spnb-unroll-limit": nodes + edges up to which a DAG is unrolled
+  int unrollLimit = 300000;    // "spnb-unroll-limit": nodes + edges up to which a DAG is unrolled
   int maxRegisters = 0;        // "spnb-max-registers"
   int gaussForm = 1;           // "spnb-gauss-form"
+  int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
   int tableWindow = 0;         // "spnb-table-window": bytes of shared memory for leaf tables (0 = 64 KB)
   std::vector<std::pair<std::string, std::string>> raw;
 };

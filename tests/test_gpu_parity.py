@@ -83,6 +83,24 @@ def _rewrap_as_query(d, path):
         f.write(data)
 
 
+def test_chunked_kernels_pass_values_through_scratch(capi, tmp_path):
+    """DAGs beyond the chunk size are emitted as several functions; values crossing a chunk boundary go
+    through per-CTA scratch memory."""
+    for idx in (1, 2, 3, 4):
+        name, spn, inputs, log_space, marginal = small_configs()[idx]
+        q = write_query(spn, marginal, directory=str(tmp_path))
+        plan_path, _ = capi.compile_query(q, _opts(log_space, spnb_kernel="unrolled", spnb_chunk_nodes=97,
+                                                   spnb_table_window=2048))
+        plan = capi.Plan(plan_path)
+        assert plan.stats["scratch_slots"] > 0 and "st.global" in plan.source
+        for n in (1, 1025, 300001):
+            x = inputs(n)
+            err = max_rel_err(plan.execute_host(x), oracle_eval(q, x, log_space))
+            assert err <= REL_TOL_F32, (name, n, err)
+        plan.close()
+        os.remove(plan_path)
+
+
 def test_streamed_table_window(capi, tmp_path):
     """Leaf tables larger than the shared-memory window are reloaded piecewise inside the kernel body."""
     for idx in (3, 4, 1):
