@@ -67,14 +67,29 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // 1024 resident threads per SM at <= 64 registers when the staged inputs of that many samples fit
   // into shared memory; otherwise the largest power-of-two CTA that fits, alone on its SM.
   int TILE = opt.tile, minBlocks = opt.minBlocksPerSM;
+  // staged codes are bytes when every discrete feature's domain (+ the two special codes) fits
+  int maxDomain = 0;
+  for (const FeatureMeta& fm : p.features)
+    if (fm.codeSlot >= 0) maxDomain = std::max(maxDomain, fm.domain);
+  const int cb = maxDomain + 2 <= 255 ? 1 : 2;
+  const size_t tabBytes = tabEntries * realBytes;
+  size_t tableLimit = (size_t)opt.smemTableLimit;
   if (TILE <= 0) {
-    const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * 2 + 4;
+    const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * cb + 4;
     size_t fixed = (size_t)d.numFeatures * 16 + 64;
-    fixed += std::min(tabEntries * realBytes, (size_t)opt.smemTableLimit) + 16;
     if (p.lut.size() <= (size_t)opt.smemTableLimit) fixed += p.lut.size();
-    const size_t budget = 200 * 1024;
-    TILE = 1024;
-    while (TILE > 64 && fixed + (size_t)(TILE + 1) * perThread > budget) TILE /= 2;
+    const size_t budget = 216 * 1024;
+    bool found = false;
+    for (TILE = 1024; TILE >= 64 && !found; TILE /= 2)
+      for (size_t w = (size_t)opt.smemTableLimit; w >= std::min<size_t>(16384, (size_t)opt.smemTableLimit) && !found; w /= 2) {
+        // a larger CTA with a smaller table window beats a smaller CTA
+        if (fixed + std::min(tabBytes, w) + 16 + (size_t)(TILE + 1) * perThread <= budget) {
+          tableLimit = w;
+          found = true;
+          TILE *= 2;  // undo the loop's step
+        }
+      }
+    if (!found) TILE = 64;
     if (minBlocks <= 0) minBlocks = 1;
   } else if (minBlocks <= 0) {
     minBlocks = std::max(1, 1024 / TILE);
@@ -84,9 +99,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // through it: leaves appear in the body in table order, so at the points where the next leaf's
   // table lies beyond the window the CTA reloads the window from global memory between two barriers.
   const bool tabSmem = tabEntries > 0;
-  const size_t tabBytes = tabEntries * realBytes;
-  const bool streamed = tabBytes > (size_t)opt.smemTableLimit;
-  const size_t winBytes = streamed ? ((size_t)opt.smemTableLimit & ~size_t(15)) : ((tabBytes + 15) & ~size_t(15));
+  const bool streamed = tabBytes > tableLimit;
+  const size_t winBytes = streamed ? (tableLimit & ~size_t(15)) : ((tabBytes + 15) & ~size_t(15));
   const bool floatIn = p.ftype.isFloat();
   const double LOG2E = 1.4426950408889634074;
   const int NV = p.numValueSlots, NC = p.numCodeSlots;
@@ -99,11 +113,11 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // values (flagged per row while the tile is staged).
   const bool twoBodies = p.marginal && floatIn && NV > 0 && p.stats.gauss > 0;
 
-  // shared memory layout (bytes): [fm int4 x NF] [xs real x NV*SX] [cs u16 x NC*SX] [tab] [lut] [nan flags int x TILE]
+  // shared memory layout (bytes): [fm int4 x NF] [xs real x NV*SX] [cs u8|u16 x NC*SX] [tab] [lut] [nan flags int x TILE]
   const size_t offFm = 0;
   const size_t offXs = identity ? 0 : (size_t)F * 16;
   const size_t offCs = offXs + (size_t)NV * SX * realBytes;
-  const size_t offTab = (offCs + (size_t)NC * SX * 2 + 15) & ~size_t(15);
+  const size_t offTab = (offCs + (size_t)NC * SX * cb + 15) & ~size_t(15);
   const size_t offLut = offTab + (tabSmem ? winBytes : 0);
   const size_t offNan = (offLut + (lutSmem ? p.lut.size() : 0) + 3) & ~size_t(3);
   const size_t smemTotal = offNan + (twoBodies ? (size_t)TILE * 4 : 0);
@@ -154,7 +168,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     return ldsStmt("real_t", ldReal, cReal, dst, "xs_t", (long long)rb * slot * SX, mergeX ? -1 : node);
   };
   auto readCode = [&](const std::string& dst, int slot, long long node) {
-    return ldsStmt("int", "ld.shared.u16", "r", dst, "cs_t", 2ll * slot * SX, node);
+    return ldsStmt("int", cb == 1 ? "ld.shared.u8" : "ld.shared.u16", "r", dst, "cs_t", (long long)cb * slot * SX, node);
   };
   long long winBase = 0;  // first table entry held by the window at the current point of the body
   auto readTab = [&](const std::string& dst, long long off, const std::string& idx, long long node) {
@@ -269,7 +283,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   o << "static __device__ __noinline__ out_t " << fname << "(const unsigned xs_s, const unsigned cs_s, const unsigned tab_s, "
        "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, uint4* __restrict__ win, "
        "real_t* __restrict__ sc, const unsigned tid)\n{\n";
-  o << "  const unsigned xs_t = xs_s + " << rb << "u * tid;\n  const unsigned cs_t = cs_s + 2u * tid;\n";
+  o << "  const unsigned xs_t = xs_s + " << rb << "u * tid;\n  const unsigned cs_t = cs_s + " << cb << "u * tid;\n";
   if (chunk == 0) {
     winBase = 0;
     if (streamed) swapWindow(o, 0);
@@ -386,7 +400,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   o << "  extern __shared__ __align__(16) unsigned char smem_raw[];\n";
   o << "  const unsigned tid = threadIdx.x;\n";
   o << "  real_t* xs = reinterpret_cast<real_t*>(smem_raw + " << offXs << ");\n";
-  o << "  unsigned short* cs = reinterpret_cast<unsigned short*>(smem_raw + " << offCs << ");\n";
+  o << "  typedef " << (cb == 1 ? "unsigned char" : "unsigned short") << " code_t;\n";
+  o << "  code_t* cs = reinterpret_cast<code_t*>(smem_raw + " << offCs << ");\n";
   o << "  const unsigned xs_s = (unsigned)__cvta_generic_to_shared(xs);\n  const unsigned cs_s = (unsigned)__cvta_generic_to_shared(cs);\n";
   o << "  unsigned tab_s = 0, lut_s = 0;\n";
   if (twoBodies) o << "  int* nanrow = reinterpret_cast<int*>(smem_raw + " << offNan << ");\n  nanrow[tid] = 0;\n";
@@ -429,7 +444,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       o << "          const unsigned rr = (unsigned)TOINT(raw) - (unsigned)m.x;\n";
       o << "          int code = rr < (unsigned)m.y ? (int)rr + 2 : 1;\n";
       if (floatIn) o << "          if (raw != raw) code = 0;\n";
-      o << "          cs[m.z * SX + r] = (unsigned short)(live ? code : 1);\n";
+      o << "          cs[m.z * SX + r] = (code_t)(live ? code : 1);\n";
       o << "        }\n";
     }
     o << "      }\n";

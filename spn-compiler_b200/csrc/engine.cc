@@ -286,7 +286,11 @@ struct Engine::DeviceState {
   int grid = 0, block = 0;
   size_t smem = 0;
   InterpArgs ia{};
-  void* dScratch = nullptr;   // per-CTA scratch of a chunked generated kernel: [grid][slots][tile] values
+  // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
+  // because launches on different streams may overlap on the GPU
+  size_t scratchBytes = 0;
+  std::map<cudaStream_t, void*> scratch;
+  std::mutex scratchMu;
   // host path
   static constexpr int kBuf = 3;
   cudaStream_t streams[kBuf] = {nullptr, nullptr, nullptr};
@@ -312,7 +316,7 @@ struct Engine::DeviceState {
     if (dProg) cudaFree(dProg);
     if (dBreaks) cudaFree(dBreaks);
     if (dMeta) cudaFree(dMeta);
-    if (dScratch) cudaFree(dScratch);
+    for (auto& kv : scratch) cudaFree(kv.second);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -398,8 +402,7 @@ Engine::DeviceState& Engine::state(int device) {
     if (perSM < 1) fail("Generated kernel does not fit on one SM");
     st->grid = perSM * st->smCount;
     if (emitInfo_.scratchSlots > 0) {
-      size_t bytes = (size_t)st->grid * emitInfo_.scratchSlots * st->block * (p.logSpace ? 4 : 8);
-      CUDA_OK(cudaMalloc(&st->dScratch, bytes));
+      st->scratchBytes = (size_t)st->grid * emitInfo_.scratchSlots * st->block * (p.logSpace ? 4 : 8);
     }
   } else {
     std::vector<int4> meta(p.features.size());
@@ -452,7 +455,18 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
   const int grid = (int)std::min<size_t>(tiles, (size_t)st.grid);
   if (strategy_ == kUnrolled) {
     unsigned long long nn = n;
-    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&st.dScratch};
+    void* dScratch = nullptr;
+    if (st.scratchBytes) {
+      std::lock_guard<std::mutex> lock(st.scratchMu);
+      auto it = st.scratch.find(stream);
+      if (it == st.scratch.end()) {
+        void* p = nullptr;
+        CUDA_OK(cudaMalloc(&p, st.scratchBytes));
+        it = st.scratch.emplace(stream, p).first;
+      }
+      dScratch = it->second;
+    }
+    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch};
     Driver& drv = Driver::get();
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
