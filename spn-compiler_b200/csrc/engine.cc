@@ -172,6 +172,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-gauss-form") o.gaussForm = std::atoi(v.c_str());
     else if (k == "spnb-table-window") o.tableWindow = std::atoi(v.c_str());
     else if (k == "spnb-chunk-nodes") o.chunkNodes = std::atoi(v.c_str());
+    else if (k == "spnb-interp-slots") o.interpSlots = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -350,6 +351,7 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->plan_ = buildPlan(e->model_, opt.logSpace);
   e->emitInfo_.kernelName = "spnb_kernel";
   e->interpTile_ = e->emitInfo_.tile;
+  e->interpSlotsCap_ = opt.interpSlots;
   e->meta_.kernelName = e->model_.name;
   e->meta_.batchSize = (uint32_t)std::max(e->model_.batchSize, 0);
   e->meta_.numFeatures = (uint32_t)e->model_.numFeatures;
@@ -408,35 +410,48 @@ Engine::DeviceState& Engine::state(int device) {
     std::vector<int4> meta(p.features.size());
     for (size_t f = 0; f < meta.size(); ++f)
       meta[f] = make_int4(p.features[f].lo, p.features[f].domain, p.features[f].codeSlot, p.features[f].valueSlot);
-    st->dProg = (int*)upload(p.prog.data(), p.prog.size() * 4);
     st->dBreaks = (int*)upload(p.groupBreaks.data(), p.groupBreaks.size() * 4);
     st->dMeta = (int4*)upload(meta.data(), meta.size() * sizeof(int4));
-    st->ia.prog = st->dProg;
     st->ia.tab = (const float*)st->dTab;
     st->ia.lut = (const unsigned char*)st->dLut;
     st->ia.breaks = st->dBreaks;
     st->ia.featureMeta = st->dMeta;
-    st->ia.progLen = (int)p.prog.size();
     st->ia.numFeatures = (int)p.features.size();
     st->ia.numValueSlots = p.numValueSlots;
     st->ia.numCodeSlots = p.numCodeSlots;
     st->ia.numSlots = p.numSlots;
     st->ia.marginal = p.marginal ? 1 : 0;
-    // largest tile whose inputs and value slots fit into the shared memory of one SM
+    // Tile and shared-memory slot count: the largest tile that leaves room for all slots, or else for
+    // at least 48 of them; the remaining slots live in global scratch memory.
     const size_t budget = (size_t)prop.sharedMemPerBlockOptin;
-    int tile = interpTile_ ? interpTile_ : 256;
-    while (tile > 32 && interpSmemBytes(st->ia, tile) > budget) tile -= 32;
-    if (interpSmemBytes(st->ia, tile) > budget)
-      fail("Model needs " + std::to_string(p.numSlots) + " live values per sample: too many for the interpreter's shared-memory slots");
-    // prefer two or more resident CTAs per SM when the tile allows it
-    if (!interpTile_)
-      while (tile > 64 && interpSmemBytes(st->ia, tile) > budget / 2 && interpSmemBytes(st->ia, tile / 2) <= budget / 2) tile /= 2;
+    const int need = p.numSlots;
+    int tile = 0, smemSlots = 0;
+    for (int t : {256, 128, 64, 32}) {
+      if (interpTile_ && t != interpTile_) continue;
+      st->ia.numSlots = 0;
+      const size_t base = interpSmemBytes(st->ia, t);
+      if (base >= budget) continue;
+      int fit = (int)std::min<size_t>((budget - base) / ((size_t)t * 4), (size_t)need);
+      if (interpSlotsCap_ > 0) fit = std::min(fit, interpSlotsCap_);
+      if (fit >= std::min(need, interpSlotsCap_ > 0 ? interpSlotsCap_ : 48)) { tile = t; smemSlots = fit; break; }
+    }
+    if (!tile) fail("The staged inputs of one warp of samples do not fit into shared memory");
+    if (smemSlots < need) {
+      std::lock_guard<std::mutex> lock(planMu_);
+      if (plan_.numSpillSlots == 0 || plan_.numSmemSlots > smemSlots) buildProgram(plan_, smemSlots);
+    }
+    st->ia.numSlots = smemSlots;
+    st->ia.numSpillSlots = plan_.numSpillSlots;
+    st->dProg = (int*)upload(plan_.prog.data(), plan_.prog.size() * 4);
+    st->ia.prog = st->dProg;
+    st->ia.progLen = (int)plan_.prog.size();
     st->block = tile;
     st->smem = interpSmemBytes(st->ia, tile);
     int perSM = 0;
     CUDA_OK(interpOccupancy(dtypeCode(p.ftype), tile, st->smem, &perSM));
     if (perSM < 1) fail("Interpreter kernel does not fit on one SM");
     st->grid = perSM * st->smCount;
+    st->scratchBytes = (size_t)st->grid * plan_.numSpillSlots * st->block * 4;
   }
   auto ins = dev_.emplace(device, std::move(st));
   return *ins.first->second;
@@ -449,29 +464,34 @@ void Engine::launchConfig(int device, int* grid, int* block, size_t* smem) {
   if (smem) *smem = st.smem;
 }
 
+// The scratch area used by launches on `stream` (allocated on first use; null if the plan needs none).
+void* Engine::scratchFor(DeviceState& st, cudaStream_t stream) {
+  if (!st.scratchBytes) return nullptr;
+  std::lock_guard<std::mutex> lock(st.scratchMu);
+  auto it = st.scratch.find(stream);
+  if (it == st.scratch.end()) {
+    void* p = nullptr;
+    CUDA_OK(cudaMalloc(&p, st.scratchBytes));
+    it = st.scratch.emplace(stream, p).first;
+  }
+  return it->second;
+}
+
 void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cudaStream_t stream) {
   if (n == 0) return;
   const size_t tiles = (n + (size_t)st.block - 1) / (size_t)st.block;
   const int grid = (int)std::min<size_t>(tiles, (size_t)st.grid);
   if (strategy_ == kUnrolled) {
     unsigned long long nn = n;
-    void* dScratch = nullptr;
-    if (st.scratchBytes) {
-      std::lock_guard<std::mutex> lock(st.scratchMu);
-      auto it = st.scratch.find(stream);
-      if (it == st.scratch.end()) {
-        void* p = nullptr;
-        CUDA_OK(cudaMalloc(&p, st.scratchBytes));
-        it = st.scratch.emplace(stream, p).first;
-      }
-      dScratch = it->second;
-    }
+    void* dScratch = scratchFor(st, stream);
     void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch};
     Driver& drv = Driver::get();
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
   } else {
-    CUDA_OK(interpLaunch(st.ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
+    InterpArgs ia = st.ia;
+    ia.scratch = (float*)scratchFor(st, stream);
+    CUDA_OK(interpLaunch(ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
   }
 }
 

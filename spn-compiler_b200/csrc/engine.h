@@ -38,6 +38,7 @@ struct Options {
   int maxRegisters = 0;        // "spnb-max-registers"
   int gaussForm = 1;           // "spnb-gauss-form"
   int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
+  int interpSlots = 0;         // "spnb-interp-slots": cap on the interpreter's shared-memory value slots (0 = as many as fit)
   int tableWindow = 0;         // "spnb-table-window": bytes of shared memory for leaf tables (0 = 64 KB)
   std::vector<std::pair<std::string, std::string>> raw;
 };
@@ -70,6 +71,7 @@ class Engine {
   Engine() = default;
   DeviceState& state(int device);
   void launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cudaStream_t stream);
+  void* scratchFor(DeviceState& st, cudaStream_t stream);
   void runHostOnDevice(int device, size_t n, const void* in, void* out, float* kernelMs);
 
   Model model_;
@@ -78,12 +80,14 @@ class Engine {
   Strategy strategy_ = kUnrolled;
   EmitInfo emitInfo_;
   int interpTile_ = 0;
+  int interpSlotsCap_ = 0;
   std::string source_;
   std::vector<char> cubin_;
   std::string statsJson_;
   int hostDevice_ = 0;
   float lastKernelMs_ = 0.f;
   std::mutex mu_;
+  std::mutex planMu_;
   std::map<int, std::unique_ptr<DeviceState>> dev_;
 };
 

@@ -96,12 +96,16 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
     const float* xcol = xs + tid;
     const unsigned short* ccol = cs + tid;
     float* v = vals + tid;
+    // value slots: ids below numSlots are shared memory, the rest this CTA's part of the scratch area
+    const int S = a.numSlots;
+    float* g = a.scratch + ((size_t)blockIdx.x * a.numSpillSlots * TILE + tid);
+    auto ld = [&](int s) -> float { return s < S ? v[s * TILE] : g[(size_t)(s - S) * TILE]; };
     int pc = 0;
     // the walk is bounded by the program length: a corrupt stream ends the tile instead of spinning
     while (pc < a.progLen) {
       const int op = __ldg(prog + pc);
       if (op == OP_END) {
-        if (tid < rows) out[base + tid] = v[__ldg(prog + pc + 1) * TILE] * 0x1.62e43p-1f;
+        if (tid < rows) out[base + tid] = ld(__ldg(prog + pc + 1)) * 0x1.62e43p-1f;
         break;
       }
       const int dst = __ldg(prog + pc + 1);
@@ -144,10 +148,10 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           float a0 = 0.0f, a1 = 0.0f;
           int i = 0;
           for (; i + 1 < k; i += 2) {
-            a0 += v[__ldg(s + i) * TILE];
-            a1 += v[__ldg(s + i + 1) * TILE];
+            a0 += ld(__ldg(s + i));
+            a1 += ld(__ldg(s + i + 1));
           }
-          if (i < k) a0 += v[__ldg(s + i) * TILE];
+          if (i < k) a0 += ld(__ldg(s + i));
           r = a0 + a1;
           pc += 3 + k;
           break;
@@ -156,15 +160,15 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           const int k = min(__ldg(prog + pc + 2), (a.progLen - pc) / 2);
           const int* s = prog + pc + 3;
           float m = __int_as_float(0xff800000);
-          for (int i = 0; i < k; ++i) m = fmaxf(m, v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)));
+          for (int i = 0; i < k; ++i) m = fmaxf(m, ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)));
           const float mm = (m == __int_as_float(0xff800000)) ? 0.0f : m;
           float acc0 = 0.0f, acc1 = 0.0f;
           int i = 0;
           for (; i + 1 < k; i += 2) {
-            acc0 += ex2(v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
-            acc1 += ex2(v[__ldg(s + 2 * i + 2) * TILE] + __int_as_float(__ldg(s + 2 * i + 3)) - mm);
+            acc0 += ex2(ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
+            acc1 += ex2(ld(__ldg(s + 2 * i + 2)) + __int_as_float(__ldg(s + 2 * i + 3)) - mm);
           }
-          if (i < k) acc0 += ex2(v[__ldg(s + 2 * i) * TILE] + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
+          if (i < k) acc0 += ex2(ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
           r = m + lg2(acc0 + acc1);
           pc += 3 + 2 * k;
           break;
@@ -173,7 +177,8 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           pc = a.progLen;
           continue;
       }
-      v[dst * TILE] = r;
+      if (dst < S) v[dst * TILE] = r;
+      else g[(size_t)(dst - S) * TILE] = r;
     }
   }
 }

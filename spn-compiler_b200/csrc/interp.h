@@ -21,7 +21,9 @@ struct InterpArgs {
   int numFeatures;
   int numValueSlots;
   int numCodeSlots;
-  int numSlots;
+  int numSlots;                 // value slots in shared memory
+  int numSpillSlots;            // value slots in the scratch area
+  float* scratch;               // device: [grid][numSpillSlots][tile] floats, or null
   int marginal;
   // byte offset of the value slots behind the staged inputs for a CTA of `tile` threads
   __host__ __device__ size_t valsOffset(unsigned tile) const {

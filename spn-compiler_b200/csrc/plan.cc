@@ -1,6 +1,7 @@
 #include "plan.h"
 
 #include <algorithm>
+#include <climits>
 #include <cmath>
 #include <cstring>
 #include <map>
@@ -196,7 +197,6 @@ Plan buildPlan(const Model& m, bool logSpace) {
   p.dag = canonicalize(m);
   Dag& d = p.dag;
   const size_t n = d.size();
-  const double LOG2E = 1.4426950408889634074;
 
   // ---- index groups, staged-feature layout and leaf tables --------------------------------------
   const int32_t F = d.numFeatures;
@@ -329,74 +329,97 @@ Plan buildPlan(const Model& m, bool logSpace) {
   s.depth = depth[n - 1];
   s.bytesPerSample = (int64_t)m.numFeatures * m.ftype.bytes() + (logSpace ? 4 : 8);
 
-  // ---- interpreter program with liveness-based slots -------------------------------------------
-  if (logSpace) {
-    std::vector<int32_t> slot(n, -1), remaining(d.uses);
-    std::vector<int32_t> freeList;
-    int32_t nslots = 0;
-    for (size_t v = 0; v < n; ++v) {
-      int64_t lo = d.childPtr[v], hi = d.childPtr[v + 1];
-      // operands are read before the result is written, so a dying operand's slot may be reused
-      for (int64_t e = lo; e < hi; ++e) {
-        int32_t c = d.childIdx[e];
-        if (--remaining[c] == 0) freeList.push_back(slot[c]);
-      }
-      int32_t dst;
-      if (!freeList.empty()) { dst = freeList.back(); freeList.pop_back(); }
-      else dst = nslots++;
-      slot[v] = dst;
-      switch (d.kind[v]) {
-        case kGaussian: {
-          double sd = d.stddev[v];
-          p.prog.push_back(OP_GAUSS);
-          p.prog.push_back(dst);
-          p.prog.push_back(p.features[d.feature[v]].valueSlot);
-          p.prog.push_back((int32_t)f32bits((float)d.mean[v]));
-          p.prog.push_back((int32_t)f32bits((float)(-(1.0 / (2.0 * sd * sd)) * LOG2E)));
-          p.prog.push_back((int32_t)f32bits((float)((-std::log(sd) - 0.5 * std::log(2 * M_PI)) * LOG2E)));
-          break;
-        }
-        case kCategorical:
-        case kHistogram: {
-          const IndexGroup& g = p.groups[d.group[v]];
-          if (g.mode == kGeneric) {
-            p.prog.push_back(OP_HISTG);
-            p.prog.push_back(dst);
-            p.prog.push_back(p.features[g.feature].valueSlot);
-            p.prog.push_back(g.brkOffset);
-            p.prog.push_back(g.count);
-            p.prog.push_back(p.tabOffset[v]);
-          } else {
-            p.prog.push_back(OP_TABLE);
-            p.prog.push_back(dst);
-            p.prog.push_back(p.features[g.feature].codeSlot);
-            p.prog.push_back(g.lutOffset);
-            p.prog.push_back(p.tabOffset[v]);
-          }
-          break;
-        }
-        case kProduct:
-          p.prog.push_back(OP_PROD);
-          p.prog.push_back(dst);
-          p.prog.push_back((int32_t)(hi - lo));
-          for (int64_t e = lo; e < hi; ++e) p.prog.push_back(slot[d.childIdx[e]]);
-          break;
-        default:
-          p.prog.push_back(OP_SUM);
-          p.prog.push_back(dst);
-          p.prog.push_back((int32_t)(hi - lo));
-          for (int64_t e = lo; e < hi; ++e) {
-            p.prog.push_back(slot[d.childIdx[e]]);
-            p.prog.push_back((int32_t)f32bits((float)std::log2(d.weight[e])));
-          }
-          break;
-      }
-    }
-    p.prog.push_back(OP_END);
-    p.prog.push_back(slot[n - 1]);
-    p.numSlots = nslots;
-  }
+  if (logSpace) buildProgram(p, INT32_MAX);
   return p;
+}
+
+// Interpreter program with liveness-based value slots.  Slots [0, smemSlots) live in shared memory,
+// the rest in a per-CTA scratch area in global memory.  A value whose live range is much longer than
+// the shared-memory capacity goes to scratch straight away: it would pin a slot that many short-lived
+// values could share.
+void buildProgram(Plan& p, int32_t smemSlots) {
+  const Dag& d = p.dag;
+  const size_t n = d.size();
+  const double LOG2E = 1.4426950408889634074;
+  p.prog.clear();
+  std::vector<int64_t> lastUse(n, -1);
+  for (size_t v = 0; v < n; ++v)
+    for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) lastUse[d.childIdx[e]] = (int64_t)v;
+  const bool limited = smemSlots != INT32_MAX;
+  const int64_t longRange = limited ? 8ll * smemSlots : INT64_MAX;
+  std::vector<int32_t> slot(n, -1), remaining(d.uses);
+  std::vector<int32_t> freeSmem, freeGlobal;
+  int32_t nSmem = 0, nGlobal = 0;
+  for (size_t v = 0; v < n; ++v) {
+    int64_t lo = d.childPtr[v], hi = d.childPtr[v + 1];
+    // operands are read before the result is written, so a dying operand's slot may be reused
+    for (int64_t e = lo; e < hi; ++e) {
+      int32_t c = d.childIdx[e];
+      if (--remaining[c] == 0) (slot[c] < smemSlots ? freeSmem : freeGlobal).push_back(slot[c]);
+    }
+    int32_t dst = -1;
+    const bool preferGlobal = limited && lastUse[v] - (int64_t)v > longRange;
+    if (!preferGlobal) {
+      if (!freeSmem.empty()) { dst = freeSmem.back(); freeSmem.pop_back(); }
+      else if (nSmem < smemSlots) dst = nSmem++;
+    }
+    if (dst < 0) {
+      if (!freeGlobal.empty()) { dst = freeGlobal.back(); freeGlobal.pop_back(); }
+      else dst = smemSlots + nGlobal++;
+    }
+    slot[v] = dst;
+    switch (d.kind[v]) {
+      case kGaussian: {
+        double sd = d.stddev[v];
+        p.prog.push_back(OP_GAUSS);
+        p.prog.push_back(dst);
+        p.prog.push_back(p.features[d.feature[v]].valueSlot);
+        p.prog.push_back((int32_t)f32bits((float)d.mean[v]));
+        p.prog.push_back((int32_t)f32bits((float)(-(1.0 / (2.0 * sd * sd)) * LOG2E)));
+        p.prog.push_back((int32_t)f32bits((float)((-std::log(sd) - 0.5 * std::log(2 * M_PI)) * LOG2E)));
+        break;
+      }
+      case kCategorical:
+      case kHistogram: {
+        const IndexGroup& g = p.groups[d.group[v]];
+        if (g.mode == kGeneric) {
+          p.prog.push_back(OP_HISTG);
+          p.prog.push_back(dst);
+          p.prog.push_back(p.features[g.feature].valueSlot);
+          p.prog.push_back(g.brkOffset);
+          p.prog.push_back(g.count);
+          p.prog.push_back(p.tabOffset[v]);
+        } else {
+          p.prog.push_back(OP_TABLE);
+          p.prog.push_back(dst);
+          p.prog.push_back(p.features[g.feature].codeSlot);
+          p.prog.push_back(g.lutOffset);
+          p.prog.push_back(p.tabOffset[v]);
+        }
+        break;
+      }
+      case kProduct:
+        p.prog.push_back(OP_PROD);
+        p.prog.push_back(dst);
+        p.prog.push_back((int32_t)(hi - lo));
+        for (int64_t e = lo; e < hi; ++e) p.prog.push_back(slot[d.childIdx[e]]);
+        break;
+      default:
+        p.prog.push_back(OP_SUM);
+        p.prog.push_back(dst);
+        p.prog.push_back((int32_t)(hi - lo));
+        for (int64_t e = lo; e < hi; ++e) {
+          p.prog.push_back(slot[d.childIdx[e]]);
+          p.prog.push_back((int32_t)f32bits((float)std::log2(d.weight[e])));
+        }
+        break;
+    }
+    }
+  p.prog.push_back(OP_END);
+  p.prog.push_back(slot[n - 1]);
+  if (!limited) p.numSlots = nSmem;
+  p.numSmemSlots = nSmem;
+  p.numSpillSlots = nGlobal;
 }
 
 }  // namespace spnb

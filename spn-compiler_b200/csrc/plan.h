@@ -98,10 +98,14 @@ struct Plan {
   // interpreter
   std::vector<int32_t> prog;
   std::vector<int32_t> groupBreaks; // breaks of the kGeneric groups
-  int32_t numSlots = 0;
+  int32_t numSlots = 0;       // slots needed when every value lives in shared memory
+  int32_t numSmemSlots = 0;   // of the current program: shared-memory slots ...
+  int32_t numSpillSlots = 0;  // ... and slots in global scratch memory (ids numSmemSlots' capacity and up)
 };
 
 Dag canonicalize(const Model& m);
 Plan buildPlan(const Model& m, bool logSpace);
+// (Re)builds Plan::prog with at most smemSlots values in shared memory (INT32_MAX: no limit).
+void buildProgram(Plan& p, int32_t smemSlots);
 
 }  // namespace spnb

@@ -229,3 +229,92 @@ def config4_inputs(n, seed=2004):
     x[:, :128] = rng.standard_normal((n, 128), dtype=np.float32)
     x[:, 128:] = rng.integers(0, 4, size=(n, 128)).astype(np.float32)
     return x
+
+
+class ArraySPN:
+    """A model held as numpy arrays (for generators that are vectorised end to end)."""
+
+    def __init__(self, num_features, feature_type, name, arrays, root):
+        self.F, self.feature_type, self.name, self.a, self.root = num_features, feature_type, name, arrays, root
+
+    @property
+    def num_nodes(self):
+        return len(self.a["kind"])
+
+    def stats(self):
+        k = self.a["kind"]
+        return {"nodes": len(k), "sums": int((k == wire.K_SUM).sum()), "products": int((k == wire.K_PRODUCT).sum()),
+                "leaves": int((k >= wire.K_HIST).sum()), "edges": len(self.a["child_id"])}
+
+    def to_xspn_bytes(self, batch_size=64, support_marginal=True, error_kind=0, max_error=0.02):
+        a = self.a
+        n = len(a["kind"])
+        z = np.zeros(n + 1, np.int64)
+        return wire.encode_flat(
+            kind=a["kind"], node_id=np.arange(n), child_ptr=a["child_ptr"], child_id=a["child_id"], weight=a["weight"],
+            scope_id=a["scope_id"], mean=a["mean"], stddev=a["stddev"], tab_ptr=z, tab=np.zeros(0), brk_ptr=z,
+            brk=np.zeros(0, np.int32), root_id=self.root, scope=list(range(self.F)), feature_type=self.feature_type,
+            name=self.name, query={"batch_size": batch_size, "error_kind": error_kind, "max_error": max_error,
+                                   "support_marginal": support_marginal})
+
+
+def config5(seed=1005, num_features=784, depth=4, repetitions=16, width=32):
+    """RAT-SPN-style layered SPN: `repetitions` random balanced region trees of depth `depth` over
+    `num_features` features; every leaf region carries `width` factorised Gaussian distributions, every
+    inner region `width` sum nodes over the width x width cross products of its two child regions (dense
+    width x width^2 weights ~ Dirichlet(1)); one root sum mixes the root products of all repetitions.
+    The full size (784, 4, 16, 32) has ~660 k nodes and ~7.4 M sum edges."""
+    rng = np.random.default_rng(seed)
+    K, F = width, num_features
+    kind, scope_id, mean, stddev, cnt, child, weight = [], [], [], [], [], [], []
+    next_id = 0
+
+    def add(k, n, counts, children, weights=None, scope=None, mu=None, sd=None):
+        nonlocal next_id
+        ids = np.arange(next_id, next_id + n, dtype=np.int64)
+        next_id += n
+        kind.append(np.full(n, k, np.int64))
+        scope_id.append(np.zeros(n, np.int64) if scope is None else scope)
+        mean.append(np.zeros(n) if mu is None else mu)
+        stddev.append(np.ones(n) if sd is None else sd)
+        cnt.append(np.asarray(counts, np.int64))
+        if children is not None:
+            child.append(np.asarray(children, np.int32).ravel())
+            weight.append(np.zeros(child[-1].size) if weights is None else np.asarray(weights, np.float64).ravel())
+        return ids
+
+    root_products = []
+    for _ in range(repetitions):
+        perm = rng.permutation(F)
+        regions = [np.sort(part) for part in np.array_split(perm, 2 ** depth)]
+        level = []
+        for feats in regions:
+            nf = len(feats)
+            g = add(wire.K_GAUSS, K * nf, np.zeros(K * nf), None, scope=np.tile(feats, K),
+                    mu=rng.normal(0.5, 0.3, K * nf), sd=rng.uniform(0.2, 1.0, K * nf))
+            level.append(add(wire.K_PRODUCT, K, np.full(K, nf), g.reshape(K, nf)))
+        for d in range(depth - 1, -1, -1):
+            nxt = []
+            for a_ids, b_ids in zip(level[0::2], level[1::2]):
+                pairs = np.stack([np.repeat(a_ids, len(b_ids)), np.tile(b_ids, len(a_ids))], axis=1)
+                prods = add(wire.K_PRODUCT, len(pairs), np.full(len(pairs), 2), pairs)
+                if d == 0:
+                    root_products.append(prods)
+                    nxt.append(prods)
+                else:
+                    w = rng.dirichlet(np.ones(len(prods)), size=K)
+                    w = np.maximum(w, 1e-9)
+                    w /= w.sum(axis=1, keepdims=True)
+                    nxt.append(add(wire.K_SUM, K, np.full(K, len(prods)), np.tile(prods, K), w))
+            level = nxt
+    allp = np.concatenate(root_products)
+    w = np.maximum(rng.dirichlet(np.ones(len(allp))), 1e-9)
+    root = add(wire.K_SUM, 1, [len(allp)], allp, w / w.sum())[0]
+    arrays = {"kind": np.concatenate(kind), "scope_id": np.concatenate(scope_id), "mean": np.concatenate(mean),
+              "stddev": np.concatenate(stddev), "child_id": np.concatenate(child), "weight": np.concatenate(weight)}
+    arrays["child_ptr"] = np.concatenate(([0], np.cumsum(np.concatenate(cnt))))
+    return ArraySPN(F, "float32", "cfg5_ratspn", arrays, int(root))
+
+
+def config5_inputs(n, seed=2005, num_features=784):
+    return np.random.default_rng(seed).random((n, num_features), dtype=np.float32)

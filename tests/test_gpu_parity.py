@@ -101,6 +101,22 @@ def test_chunked_kernels_pass_values_through_scratch(capi, tmp_path):
         os.remove(plan_path)
 
 
+def test_interpreter_spills_values_to_scratch(capi, tmp_path):
+    """With fewer shared-memory slots than live values the interpreter keeps the rest in global scratch."""
+    for idx in (2, 3, 4):
+        name, spn, inputs, log_space, marginal = small_configs()[idx]
+        q = write_query(spn, marginal, directory=str(tmp_path))
+        plan_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="interp", spnb_interp_slots=6))
+        plan = capi.Plan(plan_path)
+        assert plan.stats["interp_slots"] > 6
+        for n in (1, 257, 200001):
+            x = inputs(n)
+            err = max_rel_err(plan.execute_host(x), oracle_eval(q, x, True))
+            assert err <= REL_TOL_F32, (name, n, err)
+        plan.close()
+        os.remove(plan_path)
+
+
 def test_streamed_table_window(capi, tmp_path):
     """Leaf tables larger than the shared-memory window are reloaded piecewise inside the kernel body."""
     for idx in (3, 4, 1):
