@@ -89,6 +89,26 @@ int spnb_execute_host(spnb_plan* plan, size_t n, const void* in, void* out);
 int spnb_execute_device(spnb_plan* plan, int device, size_t n, const void* d_in, void* d_out, void* cuda_stream);
 
 /*
+ * Same contract as spnb_execute_device (device-resident in/out, asynchronous on cuda_stream), but nothing on
+ * this path allocates or frees device memory.  It has no counterpart in the reference.  It is meant for
+ * callers that may not allocate when they run a model: inside a latency-critical serving loop or any phase
+ * where cudaMalloc's device-wide synchronisation is unacceptable, or under a fixed device-memory budget
+ * agreed before start-up.  The model runs through the interpreter kernel (log-space plans only); the model
+ * image and the kernel's spill scratch live in one 32 MiB device array that is part of the library itself,
+ * so every GPU that loads the library gives up 32 MiB until the process exits.
+ *   - Limit: the plan's image (op stream + leaf tables) plus one CTA's scratch must fit into the 32 MiB;
+ *     otherwise the call fails with SPNB_ERR_RUNTIME and a message naming the limit.  n is not limited.
+ *   - The first call on a device looks up the array's device address and the first call with a given plan
+ *     copies that plan's image into the array (cudaMemcpyAsync on cuda_stream); make these first calls
+ *     before any stream capture.
+ *   - The array is shared by all plans and calls of the process and keeps the previous call's contents;
+ *     nothing in it has to be cleared.  Calls that overlap on the GPU (two streams, two threads) race on it:
+ *     order them.
+ */
+int spnb_execute_device_noalloc(spnb_plan* plan, int device, size_t n, const void* d_in, void* d_out,
+                                void* cuda_stream);
+
+/*
  * Evaluate n host-resident samples on several GPUs of this process: the batch is split into contiguous
  * row blocks, one per listed device, the model tables are replicated on each device; no collective is
  * involved.  If mean_ll_out != NULL it receives the mean log-likelihood over all n samples (summed in

@@ -108,6 +108,15 @@ int spnb_execute_device(spnb_plan* plan, int device, size_t n, const void* d_in,
   return guarded(SPNB_ERR_RUNTIME, [&] { plan->engine->executeDevice(device, n, d_in, d_out, (cudaStream_t)cuda_stream); });
 }
 
+int spnb_execute_device_noalloc(spnb_plan* plan, int device, size_t n, const void* d_in, void* d_out, void* cuda_stream) {
+  if (!plan || (n && (!d_in || !d_out))) {
+    g_lastError = "spnb_execute_device_noalloc: invalid argument";
+    return SPNB_ERR_ARGUMENT;
+  }
+  return guarded(SPNB_ERR_RUNTIME,
+                 [&] { plan->engine->executeDeviceNoAlloc(device, n, d_in, d_out, (cudaStream_t)cuda_stream); });
+}
+
 int spnb_execute_sharded(spnb_plan* plan, const int* devices, int n_devices, size_t n, const void* in, void* out,
                          double* mean_ll_out) {
   if (!plan || !devices || n_devices <= 0 || (n && (!in || !out))) {

@@ -4,6 +4,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -493,6 +494,75 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     ia.scratch = (float*)scratchFor(st, stream);
     CUDA_OK(interpLaunch(ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
   }
+}
+
+// Evaluation with no device allocation on the way: the interpreter kernel with model image and spill
+// scratch in the library's static device area (interp.cu).  Uses a private copy of the plan whose
+// program is built for the tile / slot split chosen here, so the regular path's state is untouched.
+void Engine::executeDeviceNoAlloc(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream) {
+  if (!plan_.logSpace) fail("The allocation-free entry point runs the log-space interpreter only");
+  if (n == 0) return;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+    fail("No CUDA device available: the spnb engine has no CPU fallback");
+  if (device < 0 || device >= count) fail("CUDA device " + std::to_string(device) + " does not exist");
+  int cur = -1;
+  CUDA_OK(cudaGetDevice(&cur));
+  if (cur != device) CUDA_OK(cudaSetDevice(device));
+  std::lock_guard<std::mutex> lock(noAllocMu_);
+  int optin = 0;
+  CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  if (!noAllocPlan_ || noAllocOptin_ != optin) {
+    std::unique_ptr<Plan> np(new Plan(plan_));
+    buildProgram(*np, INT32_MAX);
+    InterpArgs ia{};
+    ia.numFeatures = (int)np->features.size();
+    ia.numValueSlots = np->numValueSlots;
+    ia.numCodeSlots = np->numCodeSlots;
+    const int need = np->numSlots;
+    const int cap = interpSlotsCap_ > 0 ? interpSlotsCap_ : 48;
+    int tile = 0, smemSlots = 0;
+    for (int t : {256, 128, 64, 32}) {
+      if (interpTile_ && t != interpTile_) continue;
+      ia.numSlots = 0;
+      const size_t base = interpSmemBytes(ia, t);
+      if (base >= (size_t)optin) continue;
+      int fit = (int)std::min<size_t>(((size_t)optin - base) / ((size_t)t * 4), (size_t)need);
+      if (interpSlotsCap_ > 0) fit = std::min(fit, interpSlotsCap_);
+      if (fit >= std::min(need, cap)) { tile = t; smemSlots = fit; break; }
+    }
+    if (!tile) fail("The staged inputs of one warp of samples do not fit into shared memory");
+    if (smemSlots < need) buildProgram(*np, smemSlots);
+    noAllocMeta_.resize(np->features.size());
+    for (size_t f = 0; f < noAllocMeta_.size(); ++f)
+      noAllocMeta_[f] = make_int4(np->features[f].lo, np->features[f].domain, np->features[f].codeSlot, np->features[f].valueSlot);
+    noAllocPlan_ = std::move(np);
+    static std::atomic<unsigned long long> nextTag{1};
+    noAllocTag_ = nextTag.fetch_add(1);
+    noAllocTile_ = tile;
+    noAllocSlots_ = smemSlots;
+    noAllocOptin_ = optin;
+  }
+  const Plan& p = *noAllocPlan_;
+  InterpArgs ia{};
+  ia.progLen = (int)p.prog.size();
+  ia.numFeatures = (int)p.features.size();
+  ia.numValueSlots = p.numValueSlots;
+  ia.numCodeSlots = p.numCodeSlots;
+  ia.numSlots = noAllocSlots_;
+  ia.numSpillSlots = p.numSpillSlots;
+  ia.marginal = p.marginal ? 1 : 0;
+  InterpImage img;
+  img.prog = p.prog.data();         img.progBytes = p.prog.size() * 4;
+  img.tab = p.tabF32.data();        img.tabBytes = p.tabF32.size() * 4;
+  img.lut = p.lut.data();           img.lutBytes = p.lut.size();
+  img.breaks = p.groupBreaks.data(); img.breaksBytes = p.groupBreaks.size() * 4;
+  img.meta = noAllocMeta_.data();   img.metaBytes = noAllocMeta_.size() * sizeof(int4);
+  img.tag = noAllocTag_;
+  const char* why = nullptr;
+  cudaError_t e = interpLaunchStatic(img, ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, noAllocTile_, device, stream, &why);
+  if (cur != device && cur >= 0) cudaSetDevice(cur);
+  if (e != cudaSuccess) fail(why ? std::string("spnb_execute_device_noalloc: ") + why : std::string("CUDA error: ") + cudaGetErrorString(e));
 }
 
 void Engine::executeDevice(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream) {

@@ -61,6 +61,7 @@ class Engine {
 
   void executeHost(size_t n, const void* in, void* out);
   void executeDevice(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream);
+  void executeDeviceNoAlloc(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream);
   void executeSharded(const int* devices, int nDevices, size_t n, const void* in, void* out, double* meanOut);
   void setDevice(int device) { hostDevice_ = device; }
   void launchConfig(int device, int* grid, int* block, size_t* smem);
@@ -88,6 +89,12 @@ class Engine {
   float lastKernelMs_ = 0.f;
   std::mutex mu_;
   std::mutex planMu_;
+  // allocation-free path (executeDeviceNoAlloc)
+  std::mutex noAllocMu_;
+  std::unique_ptr<Plan> noAllocPlan_;
+  std::vector<int4> noAllocMeta_;
+  int noAllocTile_ = 0, noAllocSlots_ = 0, noAllocOptin_ = 0;
+  unsigned long long noAllocTag_ = 0;
   std::map<int, std::unique_ptr<DeviceState>> dev_;
 };
 

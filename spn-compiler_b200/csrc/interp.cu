@@ -10,6 +10,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+#include <mutex>
+
 #include "interp.h"
 
 namespace spnb {
@@ -225,6 +228,99 @@ cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, flo
     case DT_F64: return launchT<double>(a, in, out, n, grid, tile, smem, stream);
     default: return cudaErrorInvalidValue;
   }
+}
+
+// =========================================================================================================
+// Interpreter without device allocations.
+//
+// Some callers must not allocate device memory at the time they run a model: code inside a CUDA-graph
+// capture or a latency-critical serving loop (cudaMalloc synchronises the device and is illegal during
+// capture), and hosts that hand this library a fixed memory budget up front.  For them the interpreter
+// can run with everything it needs besides the caller's input and output buffers placed in one
+// file-scope device array: first the model image (op stream, leaf tables, byte tables, breaks, feature
+// descriptors), then the per-CTA spill scratch.  The array's size is fixed (kStaticAreaBytes); a model
+// whose image plus one CTA's scratch does not fit is rejected.  The grid shrinks, if necessary, to as
+// many CTAs as the scratch left over can serve.
+//
+// The array is shared by every call in the process and keeps whatever the last call left in it.  Nothing
+// in it needs to start at zero: the image is rewritten when a different plan ran last, and every scratch
+// slot is written before it is read within one tile.  Two calls that overlap on the GPU (different
+// streams, or different host threads) race on it: callers must order them.
+// =========================================================================================================
+namespace {
+
+static __device__ __align__(256) unsigned char g_staticArea[kStaticAreaBytes];
+
+struct StaticAreaState {
+  unsigned char* base = nullptr;      // device address of g_staticArea on this device
+  unsigned long long resident = 0;    // tag of the image currently stored there
+};
+StaticAreaState g_areaState[64];
+std::mutex g_areaMutex;
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+}  // namespace
+
+cudaError_t interpLaunchStatic(const InterpImage& img, InterpArgs a, int dtypeCode, const void* in, float* out, size_t n,
+                               int tile, int device, cudaStream_t stream, const char** message) {
+  if (message) *message = nullptr;
+  if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_areaMutex);
+  StaticAreaState& st = g_areaState[device];
+  if (!st.base) {
+    // In host code the array's name is only a handle; the kernel needs the address on this device.
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_staticArea);
+    if (e != cudaSuccess) return e;
+    st.base = static_cast<unsigned char*>(p);
+  }
+  const size_t offProg = 0;
+  const size_t offTab = offProg + align256(img.progBytes);
+  const size_t offLut = offTab + align256(img.tabBytes);
+  const size_t offBrk = offLut + align256(img.lutBytes);
+  const size_t offMeta = offBrk + align256(img.breaksBytes);
+  const size_t offScratch = offMeta + align256(img.metaBytes);
+  const size_t perCta = (size_t)a.numSpillSlots * (size_t)tile * sizeof(float);
+  if (offScratch + perCta > kStaticAreaBytes) {
+    if (message) *message = "model image and one CTA of spill scratch exceed the static device area (32 MiB)";
+    return cudaErrorInvalidValue;
+  }
+  if (st.resident != img.tag) {
+    cudaError_t e = cudaSuccess;
+    auto put = [&](size_t off, const void* src, size_t bytes) {
+      if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(st.base + off, src, bytes, cudaMemcpyHostToDevice, stream);
+    };
+    put(offProg, img.prog, img.progBytes);
+    put(offTab, img.tab, img.tabBytes);
+    put(offLut, img.lut, img.lutBytes);
+    put(offBrk, img.breaks, img.breaksBytes);
+    put(offMeta, img.meta, img.metaBytes);
+    if (e != cudaSuccess) { st.resident = 0; return e; }
+    st.resident = img.tag;
+  }
+  a.prog = reinterpret_cast<const int*>(st.base + offProg);
+  a.tab = reinterpret_cast<const float*>(st.base + offTab);
+  a.lut = st.base + offLut;
+  a.breaks = reinterpret_cast<const int*>(st.base + offBrk);
+  a.featureMeta = reinterpret_cast<const int4*>(st.base + offMeta);
+  a.scratch = reinterpret_cast<float*>(st.base + offScratch);
+  const size_t smem = interpSmemBytes(a, tile);
+  int perSM = 0, sms = 0;
+  cudaError_t e = interpOccupancy(dtypeCode, tile, smem, &perSM);
+  if (e != cudaSuccess) return e;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (e != cudaSuccess) return e;
+  if (perSM < 1) {
+    if (message) *message = "interpreter kernel does not fit on one SM with this tile";
+    return cudaErrorInvalidValue;
+  }
+  size_t grid = (size_t)perSM * (size_t)sms;
+  if (perCta) grid = std::min(grid, (kStaticAreaBytes - offScratch) / perCta);
+  const size_t tiles = (n + (size_t)tile - 1) / (size_t)tile;
+  grid = std::min(grid, tiles);
+  if (grid == 0) return cudaSuccess;
+  return interpLaunch(a, dtypeCode, in, out, n, (int)grid, tile, smem, stream);
 }
 
 }  // namespace spnb

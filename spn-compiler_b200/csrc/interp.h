@@ -38,4 +38,26 @@ cudaError_t interpOccupancy(int dtypeCode, int tile, size_t smem, int* blocksPer
 cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
                          size_t smem, cudaStream_t stream);
 
+// ---- variant without device allocations ---------------------------------------------------------------
+// Size of the file-scope device area that holds the model image and the spill scratch of
+// interpLaunchStatic.  Every GPU that loads the library keeps this much memory until the process exits.
+constexpr size_t kStaticAreaBytes = 32u << 20;
+
+// Host copies of everything the interpreter reads on the device besides inputs and outputs.
+struct InterpImage {
+  const void* prog = nullptr;   size_t progBytes = 0;
+  const void* tab = nullptr;    size_t tabBytes = 0;
+  const void* lut = nullptr;    size_t lutBytes = 0;
+  const void* breaks = nullptr; size_t breaksBytes = 0;
+  const void* meta = nullptr;   size_t metaBytes = 0;
+  unsigned long long tag = 0;   // identifies the image; a different tag forces a new upload
+};
+
+// Runs the interpreter with its model image and spill scratch inside the static device area: no
+// cudaMalloc / cudaFree anywhere on this path.  `a` carries the counts (pointers are filled in here).
+// Returns cudaSuccess or an error; *message (if not null) receives a static explanation for
+// capacity errors.
+cudaError_t interpLaunchStatic(const InterpImage& img, InterpArgs a, int dtypeCode, const void* in, float* out, size_t n,
+                               int tile, int device, cudaStream_t stream, const char** message);
+
 }  // namespace spnb

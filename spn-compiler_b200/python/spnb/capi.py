@@ -34,6 +34,7 @@ def _load():
         "spnb_plan_source": (cp, [vp]),
         "spnb_execute_host": (ctypes.c_int, [vp, sz, vp, vp]),
         "spnb_execute_device": (ctypes.c_int, [vp, ctypes.c_int, sz, vp, vp, vp]),
+        "spnb_execute_device_noalloc": (ctypes.c_int, [vp, ctypes.c_int, sz, vp, vp, vp]),
         "spnb_execute_sharded": (ctypes.c_int, [vp, ctypes.POINTER(ctypes.c_int), ctypes.c_int, sz, vp, vp,
                                                 ctypes.POINTER(ctypes.c_double)]),
         "spnb_set_device": (ctypes.c_int, [vp, ctypes.c_int]),
@@ -54,7 +55,7 @@ def _load():
 
 lib = _load()
 EXPORTS = ["spnb_compile", "spnb_plan_load", "spnb_plan_info", "spnb_plan_stats_json", "spnb_plan_source",
-           "spnb_execute_host", "spnb_execute_device", "spnb_execute_sharded", "spnb_set_device",
+           "spnb_execute_host", "spnb_execute_device", "spnb_execute_device_noalloc", "spnb_execute_sharded", "spnb_set_device",
            "spnb_launch_config", "spnb_last_kernel_ms", "spnb_plan_free", "spnb_measure_peak", "spnb_device_count", "spnb_last_error",
            "spnb_version"]
 
@@ -124,6 +125,10 @@ class Plan:
 
     def execute_device(self, device, n, d_in, d_out, stream=0):
         _check(lib.spnb_execute_device(self._h, device, n, d_in, d_out, stream))
+
+    def execute_device_noalloc(self, device, n, d_in, d_out, stream=0):
+        """Like execute_device, but through the entry point that never allocates device memory."""
+        _check(lib.spnb_execute_device_noalloc(self._h, device, n, d_in, d_out, stream))
 
     def execute_sharded(self, devices, inputs, want_mean=False):
         x = np.ascontiguousarray(inputs)
