@@ -41,6 +41,8 @@ CONFIGS = {
             log_space=True, marginal=True),
     4: dict(name="cfg4: 256 mixed features, ~50000-node DAG, f32 log-space (interpreter)", n=4_000_000,
             log_space=True, marginal=True),
+    5: dict(name="cfg5: RAT-SPN-style layered SPN, 784 Gaussian features, 16 repetitions, 32x1024 dense sums, f32 log-space",
+            n=2_000_000, log_space=True, marginal=True),
 }
 
 
@@ -52,7 +54,7 @@ def build_workload(cfg_id, workdir):
     with open(path, "wb") as f:
         f.write(spn.to_xspn_bytes(support_marginal=CONFIGS[cfg_id]["marginal"]))
     gen = {1: lambda n, seed: synth.config1_inputs(spn, n, seed), 2: synth.config2_inputs, 3: synth.config3_inputs,
-           4: synth.config4_inputs}[cfg_id]
+           4: synth.config4_inputs, 5: synth.config5_inputs}[cfg_id]
     return path, gen
 
 

@@ -17,6 +17,8 @@
 
 #include "interp.h"
 #include "jit.h"
+#include "layered.h"
+#include "layers.h"
 
 namespace spnb {
 
@@ -115,7 +117,7 @@ std::string makeStatsJson(const Plan& p, Strategy s, const EmitInfo& ei, int reg
   std::string base = p.stats.toJson();
   base.pop_back();
   o << base << ",\"log_space\":" << (p.logSpace ? "true" : "false") << ",\"strategy\":\""
-    << (s == kUnrolled ? "unrolled" : "interpreter") << "\",\"tile\":" << ei.tile << ",\"registers\":" << regs
+    << (s == kUnrolled ? "unrolled" : (s == kInterpreter ? "interpreter" : "layered")) << "\",\"tile\":" << ei.tile << ",\"registers\":" << regs
     << ",\"spill_bytes\":" << spill << ",\"smem_bytes\":" << ei.dynamicSmemBytes << ",\"interp_slots\":" << interpSlots
     << ",\"scratch_slots\":" << ei.scratchSlots << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
   return o.str();
@@ -163,7 +165,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "graph-stats-file") o.statsFile = v;
     else if (k == "optLevel") o.optLevel = std::atoi(v.c_str());
     else if (k == "spnb-kernel") {
-      if (v != "auto" && v != "unrolled" && v != "interp") fail("Unknown value '" + v + "' for option spnb-kernel");
+      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered") fail("Unknown value '" + v + "' for option spnb-kernel");
       o.kernelMode = v;
     } else if (k == "spnb-tile") o.tile = std::atoi(v.c_str());
     else if (k == "spnb-min-blocks") o.minBlocks = std::atoi(v.c_str());
@@ -192,7 +194,11 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
 
   Strategy strat;
   const int64_t size = plan.stats.nodes + plan.stats.sumEdges + plan.stats.productEdges;
-  if (opt.kernelMode == "unrolled") strat = kUnrolled;
+  LayeredPlan layered;
+  if (opt.kernelMode == "layered") {
+    if (!opt.logSpace || !recogniseLayers(plan.dag, &layered)) fail("spnb-kernel=layered needs a log-space query whose DAG is a layered (RAT-SPN-style) region graph");
+    strat = kLayered;
+  } else if (opt.kernelMode == "unrolled") strat = kUnrolled;
   else if (opt.kernelMode == "interp") strat = kInterpreter;
   else {
     // very wide sums unroll into code the JIT takes minutes to digest; the interpreter's inner
@@ -201,6 +207,8 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     for (size_t v = 0; v < plan.dag.size(); ++v)
       if (plan.dag.kind[v] == kSum) maxFanIn = std::max<int64_t>(maxFanIn, plan.dag.childPtr[v + 1] - plan.dag.childPtr[v]);
     strat = (size <= opt.unrollLimit && (maxFanIn <= 64 || !opt.logSpace)) ? kUnrolled : kInterpreter;
+    // dense layered models too large to unroll get the layered kernel instead of the interpreter
+    if (strat == kInterpreter && opt.logSpace && recogniseLayers(plan.dag, &layered)) strat = kLayered;
   }
   if (strat == kInterpreter && !opt.logSpace)
     fail("The interpreter kernel evaluates in log space only; pass use-log-space=true for a DAG of this size");
@@ -288,6 +296,11 @@ struct Engine::DeviceState {
   int grid = 0, block = 0;
   size_t smem = 0;
   InterpArgs ia{};
+  LayeredArgs la{};
+  void* dSteps = nullptr;
+  void* dFeat = nullptr;
+  void* dQuad = nullptr;
+  void* dWeights = nullptr;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
   // because launches on different streams may overlap on the GPU
   size_t scratchBytes = 0;
@@ -319,6 +332,10 @@ struct Engine::DeviceState {
     if (dBreaks) cudaFree(dBreaks);
     if (dMeta) cudaFree(dMeta);
     for (auto& kv : scratch) cudaFree(kv.second);
+    if (dSteps) cudaFree(dSteps);
+    if (dFeat) cudaFree(dFeat);
+    if (dQuad) cudaFree(dQuad);
+    if (dWeights) cudaFree(dWeights);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -407,6 +424,35 @@ Engine::DeviceState& Engine::state(int device) {
     if (emitInfo_.scratchSlots > 0) {
       st->scratchBytes = (size_t)st->grid * emitInfo_.scratchSlots * st->block * (p.logSpace ? 4 : 8);
     }
+  } else if (strategy_ == kLayered) {
+    LayeredPlan lp;
+    if (!recogniseLayers(p.dag, &lp)) fail("plan file says layered, but the model is not");
+    std::vector<LayerStepDev> steps(lp.steps.size());
+    for (size_t i = 0; i < steps.size(); ++i) {
+      const LayerStep& s = lp.steps[i];
+      steps[i] = LayerStepDev{s.op, s.width, s.wa, s.wb, s.numFeatures, (int)s.featOffset, 0, 0, (long long)s.paramOffset, 0};
+    }
+    st->dSteps = upload(steps.data(), steps.size() * sizeof(LayerStepDev));
+    st->dFeat = upload(lp.features.data(), lp.features.size() * 4);
+    st->dQuad = upload(lp.quad.data(), lp.quad.size() * 4);
+    st->dWeights = upload(lp.weights.data(), lp.weights.size() * 4);
+    st->la.steps = (const LayerStepDev*)st->dSteps;
+    st->la.features = (const int*)st->dFeat;
+    st->la.quad = (const float4*)st->dQuad;
+    st->la.weights = (const float*)st->dWeights;
+    st->la.numSteps = (int)steps.size();
+    st->la.numInputFeatures = (int)p.features.size();
+    st->la.maxDepth = lp.maxDepth;
+    st->la.maxLeafFeatures = lp.maxLeafFeatures;
+    st->la.marginal = (p.marginal && p.ftype.isFloat()) ? 1 : 0;
+    int tile = interpTile_ ? interpTile_ : 128;
+    while (tile > 32 && layeredSmemBytes(st->la, tile) > (size_t)prop.sharedMemPerBlockOptin) tile /= 2;
+    st->block = tile;
+    st->smem = layeredSmemBytes(st->la, tile);
+    int perSM = 0;
+    CUDA_OK(layeredOccupancy(tile, st->smem, &perSM));
+    if (perSM < 1) fail("Layered kernel does not fit on one SM");
+    st->grid = perSM * st->smCount;
   } else {
     std::vector<int4> meta(p.features.size());
     for (size_t f = 0; f < meta.size(); ++f)
@@ -489,6 +535,8 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     Driver& drv = Driver::get();
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
+  } else if (strategy_ == kLayered) {
+    CUDA_OK(layeredLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
   } else {
     InterpArgs ia = st.ia;
     ia.scratch = (float*)scratchFor(st, stream);

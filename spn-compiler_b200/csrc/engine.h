@@ -45,7 +45,7 @@ struct Options {
 
 Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv);
 
-enum Strategy : int32_t { kUnrolled = 0, kInterpreter = 1 };
+enum Strategy : int32_t { kUnrolled = 0, kInterpreter = 1, kLayered = 2 };
 
 class Engine {
  public:
