@@ -70,12 +70,21 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
           float m = 1.f;
           if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
           const float4* p = pbuf + f * s.width;
+          if (s.width == KMAX) {   // full-width region: no guards, the 32 chains interleave freely
 #pragma unroll
-          for (int k = 0; k < KMAX; ++k) {
-            if (k < s.width) {
+            for (int k = 0; k < KMAX; ++k) {
               const float4 q = p[k];
               const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
               acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k) {
+              if (k < s.width) {
+                const float4 q = p[k];
+                const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+              }
             }
           }
         }
@@ -111,7 +120,26 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
           for (int i = tid; i < per; i += T) wbuf[i] = __ldg(w + i);
           __syncthreads();
           float acc = 0.f;
-          if ((s.wb & 3) == 0) {
+          if (s.wa == KMAX && s.wb == KMAX) {
+            // full 32 x 32 block: four independent partial sums per row, rows unrolled without guards
+            float acc2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < KMAX; ++i) {
+              const float4* wr = reinterpret_cast<const float4*>(wbuf + i * KMAX);
+              float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+#pragma unroll
+              for (int j = 0; j < KMAX / 4; ++j) {
+                const float4 q = wr[j];
+                t0 = fmaf(q.x, eb[4 * j], t0);
+                t1 = fmaf(q.y, eb[4 * j + 1], t1);
+                t2 = fmaf(q.z, eb[4 * j + 2], t2);
+                t3 = fmaf(q.w, eb[4 * j + 3], t3);
+              }
+              if (i & 1) acc2 = fmaf(ea[i], (t0 + t1) + (t2 + t3), acc2);
+              else acc = fmaf(ea[i], (t0 + t1) + (t2 + t3), acc);
+            }
+            acc += acc2;
+          } else if ((s.wb & 3) == 0) {
 #pragma unroll
             for (int i = 0; i < KMAX; ++i) {
               if (i < s.wa) {
