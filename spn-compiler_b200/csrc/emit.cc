@@ -75,13 +75,14 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const size_t tabBytes = tabEntries * realBytes;
   size_t tableLimit = (size_t)opt.smemTableLimit;
   if (TILE <= 0) {
-    const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * cb + 4;
+    const bool nanFlags = p.marginal && p.ftype.isFloat() && p.numValueSlots > 0 && p.stats.gauss > 0;
+    const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * cb + (nanFlags ? 4 : 0);
     size_t fixed = (size_t)d.numFeatures * 16 + 64;
     if (p.lut.size() <= (size_t)opt.smemTableLimit) fixed += p.lut.size();
-    const size_t budget = 216 * 1024;
+    const size_t budget = 226 * 1024;  // one CTA may use up to 227 KB
     bool found = false;
     for (TILE = 1024; TILE >= 64 && !found; TILE /= 2)
-      for (size_t w = (size_t)opt.smemTableLimit; w >= std::min<size_t>(16384, (size_t)opt.smemTableLimit) && !found; w /= 2) {
+      for (size_t w = (size_t)opt.smemTableLimit; w >= std::min<size_t>(8192, (size_t)opt.smemTableLimit) && !found; w /= 2) {
         // a larger CTA with a smaller table window beats a smaller CTA
         if (fixed + std::min(tabBytes, w) + 16 + (size_t)(TILE + 1) * perThread <= budget) {
           tableLimit = w;

@@ -1,6 +1,7 @@
 #include "engine.h"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -165,7 +166,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "graph-stats-file") o.statsFile = v;
     else if (k == "optLevel") o.optLevel = std::atoi(v.c_str());
     else if (k == "spnb-kernel") {
-      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered") fail("Unknown value '" + v + "' for option spnb-kernel");
+      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar") fail("Unknown value '" + v + "' for option spnb-kernel");
       o.kernelMode = v;
     } else if (k == "spnb-tile") o.tile = std::atoi(v.c_str());
     else if (k == "spnb-min-blocks") o.minBlocks = std::atoi(v.c_str());
@@ -176,6 +177,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-table-window") o.tableWindow = std::atoi(v.c_str());
     else if (k == "spnb-chunk-nodes") o.chunkNodes = std::atoi(v.c_str());
     else if (k == "spnb-interp-slots") o.interpSlots = std::atoi(v.c_str());
+    else if (k == "spnb-mma-split") o.mmaSplit = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -195,7 +197,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   Strategy strat;
   const int64_t size = plan.stats.nodes + plan.stats.sumEdges + plan.stats.productEdges;
   LayeredPlan layered;
-  if (opt.kernelMode == "layered") {
+  if (opt.kernelMode == "layered" || opt.kernelMode == "layered-scalar") {
     if (!opt.logSpace || !recogniseLayers(plan.dag, &layered)) fail("spnb-kernel=layered needs a log-space query whose DAG is a layered (RAT-SPN-style) region graph");
     strat = kLayered;
   } else if (opt.kernelMode == "unrolled") strat = kUnrolled;
@@ -301,6 +303,10 @@ struct Engine::DeviceState {
   void* dFeat = nullptr;
   void* dQuad = nullptr;
   void* dWeights = nullptr;
+  void* dMma = nullptr;
+  void* dFrags = nullptr;
+  void* dScales = nullptr;
+  bool useMma = false;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
   // because launches on different streams may overlap on the GPU
   size_t scratchBytes = 0;
@@ -336,6 +342,9 @@ struct Engine::DeviceState {
     if (dFeat) cudaFree(dFeat);
     if (dQuad) cudaFree(dQuad);
     if (dWeights) cudaFree(dWeights);
+    if (dMma) cudaFree(dMma);
+    if (dFrags) cudaFree(dFrags);
+    if (dScales) cudaFree(dScales);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -370,6 +379,8 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->emitInfo_.kernelName = "spnb_kernel";
   e->interpTile_ = e->emitInfo_.tile;
   e->interpSlotsCap_ = opt.interpSlots;
+  e->layeredScalar_ = opt.kernelMode == "layered-scalar";
+  e->mmaSplit_ = opt.mmaSplit != 0;
   e->meta_.kernelName = e->model_.name;
   e->meta_.batchSize = (uint32_t)std::max(e->model_.batchSize, 0);
   e->meta_.numFeatures = (uint32_t)e->model_.numFeatures;
@@ -445,14 +456,76 @@ Engine::DeviceState& Engine::state(int device) {
     st->la.maxDepth = lp.maxDepth;
     st->la.maxLeafFeatures = lp.maxLeafFeatures;
     st->la.marginal = (p.marginal && p.ftype.isFloat()) ? 1 : 0;
-    int tile = interpTile_ ? interpTile_ : 128;
-    while (tile > 32 && layeredSmemBytes(st->la, tile) > (size_t)prop.sharedMemPerBlockOptin) tile /= 2;
-    st->block = tile;
-    st->smem = layeredSmemBytes(st->la, tile);
-    int perSM = 0;
-    CUDA_OK(layeredOccupancy(tile, st->smem, &perSM));
-    if (perSM < 1) fail("Layered kernel does not fit on one SM");
-    st->grid = perSM * st->smCount;
+    // Tensor-core path: every full-width region (32 x 32 cross products) gets its weights as half-precision
+    // mma.sync B fragments, [k-step][n-tile][lane] x {k, k+1, k+8, k+9}, rows scaled by their largest weight.
+    std::vector<MmaRegionDev> mma(steps.size(), MmaRegionDev{-1, 0, 0});
+    std::vector<uint2> frags;
+    std::vector<float> scales;
+    bool anyMma = false;
+    if (!layeredScalar_) {
+      for (size_t i = 0; i < steps.size(); ++i) {
+        const LayerStep& s = lp.steps[i];
+        if (s.op == kLeafRegion || s.wa != 32 || s.wb != 32 || s.width > 32) continue;
+        const int nt = (s.width + 7) / 8;
+        mma[i].fragOffset = (long long)frags.size();
+        mma[i].scaleOffset = (int)scales.size();
+        mma[i].numTiles = nt;
+        const float* W = lp.weights.data() + s.paramOffset;
+        std::vector<float> inv((size_t)nt * 8, 0.f);
+        for (int k = 0; k < nt * 8; ++k) {
+          float mx = 0.f;
+          if (k < s.width) for (int q = 0; q < 1024; ++q) mx = std::max(mx, W[(size_t)k * 1024 + q]);
+          inv[(size_t)k] = mx > 0.f ? 1.f / mx : 0.f;
+          scales.push_back(mx > 0.f ? std::log2(mx) : -INFINITY);
+        }
+        auto h16 = [&](int k, int kk, bool residue) -> unsigned {
+          const float v = k < s.width ? W[(size_t)k * 1024 + kk] * inv[(size_t)k] : 0.f;
+          __half h = __float2half_rn(v);
+          if (residue) h = __float2half_rn(v - __half2float(h));
+          unsigned short bits;
+          std::memcpy(&bits, &h, 2);
+          return bits;
+        };
+        for (int ks = 0; ks < 64; ++ks)
+          for (int t = 0; t < nt; ++t)
+            for (int lane = 0; lane < 32; ++lane) {
+              const int g = lane >> 2, tig = lane & 3, k = 8 * t + g, kk = 16 * ks + 2 * tig;
+              for (int residue = 0; residue < (mmaSplit_ ? 2 : 1); ++residue) {
+                uint2 f;
+                f.x = h16(k, kk, residue) | (h16(k, kk + 1, residue) << 16);
+                f.y = h16(k, kk + 8, residue) | (h16(k, kk + 9, residue) << 16);
+                frags.push_back(f);
+              }
+            }
+        anyMma = true;
+      }
+    }
+    if (anyMma) {
+      st->dMma = upload(mma.data(), mma.size() * sizeof(MmaRegionDev));
+      st->dFrags = upload(frags.data(), frags.size() * sizeof(uint2));
+      st->dScales = upload(scales.data(), scales.size() * 4);
+      st->la.mma = (const MmaRegionDev*)st->dMma;
+      st->la.frags = (const uint2*)st->dFrags;
+      st->la.scales = (const float*)st->dScales;
+      st->la.split = mmaSplit_ ? 1 : 0;
+      st->useMma = true;
+      st->block = 256;
+      st->smem = layeredMmaSmemBytes(st->la);
+      if (st->smem > (size_t)prop.sharedMemPerBlockOptin) fail("Layered tensor-core kernel: region stack too deep for shared memory");
+      int perSM = 0;
+      CUDA_OK(layeredMmaOccupancy(st->smem, &perSM));
+      if (perSM < 1) fail("Layered tensor-core kernel does not fit on one SM");
+      st->grid = perSM * st->smCount;
+    } else {
+      int tile = interpTile_ ? interpTile_ : 128;
+      while (tile > 32 && layeredSmemBytes(st->la, tile) > (size_t)prop.sharedMemPerBlockOptin) tile /= 2;
+      st->block = tile;
+      st->smem = layeredSmemBytes(st->la, tile);
+      int perSM = 0;
+      CUDA_OK(layeredOccupancy(tile, st->smem, &perSM));
+      if (perSM < 1) fail("Layered kernel does not fit on one SM");
+      st->grid = perSM * st->smCount;
+    }
   } else {
     std::vector<int4> meta(p.features.size());
     for (size_t f = 0; f < meta.size(); ++f)
@@ -536,7 +609,8 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
   } else if (strategy_ == kLayered) {
-    CUDA_OK(layeredLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
+    if (st.useMma) CUDA_OK(layeredMmaLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.smem, stream));
+    else CUDA_OK(layeredLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
   } else {
     InterpArgs ia = st.ia;
     ia.scratch = (float*)scratchFor(st, stream);

@@ -38,6 +38,7 @@ struct Options {
   int maxRegisters = 0;        // "spnb-max-registers"
   int gaussForm = 1;           // "spnb-gauss-form"
   int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
+  int mmaSplit = 1;            // "spnb-mma-split": 1 = half-precision operands carry their rounding residue (3 MMAs), 0 = plain fp16
   int interpSlots = 0;         // "spnb-interp-slots": cap on the interpreter's shared-memory value slots (0 = as many as fit)
   int tableWindow = 0;         // "spnb-table-window": bytes of shared memory for leaf tables (0 = 64 KB)
   std::vector<std::pair<std::string, std::string>> raw;
@@ -82,6 +83,8 @@ class Engine {
   EmitInfo emitInfo_;
   int interpTile_ = 0;
   int interpSlotsCap_ = 0;
+  bool layeredScalar_ = false;
+  bool mmaSplit_ = true;
   std::string source_;
   std::vector<char> cubin_;
   std::string statsJson_;

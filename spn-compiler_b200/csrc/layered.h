@@ -12,6 +12,15 @@ struct LayerStepDev {
   long long pad2;
 };
 
+// Description of one dense region for the tensor-core path: its weights are stored as half-precision
+// mma.sync B fragments, [k-step][n-tile][lane] x 4 halves, each sum's row divided by its largest weight
+// (the base-2 log of that divisor is added back after the contraction).
+struct MmaRegionDev {
+  long long fragOffset;   // first uint2 (4 halves) of the region's fragments
+  int scaleOffset;        // first float of the per-sum log2 scale
+  int numTiles;           // n-tiles of 8 sums
+};
+
 struct LayeredArgs {
   const LayerStepDev* steps;
   const int* features;
@@ -22,11 +31,23 @@ struct LayeredArgs {
   int maxDepth;
   int maxLeafFeatures;
   int marginal;
+  // tensor-core path (null / 0 when absent)
+  const MmaRegionDev* mma;     // per step; fragOffset < 0: the step has no fragments (scalar code runs it)
+  const uint2* frags;
+  const float* scales;
+  int split;                   // 1: fragments come in (value, residue) pairs and three MMAs are issued per pair
 };
 
 size_t layeredSmemBytes(const LayeredArgs& a, int tile);
 cudaError_t layeredLaunch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
                           size_t smem, cudaStream_t stream);
 cudaError_t layeredOccupancy(int tile, size_t smem, int* blocksPerSM);
+
+// Tensor-core version: CTAs of 256 samples, dense 32 x (32*32) regions contracted with mma.sync (fp16 in,
+// fp32 accumulate); everything else as in the scalar kernel.
+size_t layeredMmaSmemBytes(const LayeredArgs& a);
+cudaError_t layeredMmaLaunch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid,
+                             size_t smem, cudaStream_t stream);
+cudaError_t layeredMmaOccupancy(size_t smem, int* blocksPerSM);
 
 }  // namespace spnb

@@ -124,27 +124,27 @@ def test_layered_ratspn_kernel(capi, tmp_path):
     shapes = [dict(num_features=64, depth=2, repetitions=3, width=4),
               dict(num_features=96, depth=3, repetitions=2, width=8),
               dict(num_features=70, depth=1, repetitions=2, width=32),
-              dict(num_features=50, depth=2, repetitions=2, width=6)]   # width not a multiple of four
+              dict(num_features=50, depth=2, repetitions=2, width=6),    # width not a multiple of four
+              dict(num_features=192, depth=2, repetitions=2, width=32)]  # full-width regions: tensor-core path
     for sh in shapes:
         spn = synth.config5(seed=7, **sh)
         q = write_query(spn, True, directory=str(tmp_path))
-        plan_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="layered"))
-        plan = capi.Plan(plan_path)
-        assert plan.stats["strategy"] == "layered"
-        ip_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="interp"))
-        interp = capi.Plan(ip_path)
+        plans = {}
+        for mode in ("layered", "layered-scalar", "interp"):
+            path, _ = capi.compile_query(q, _opts(True, spnb_kernel=mode))
+            plans[mode] = (capi.Plan(path), path)
+        assert plans["layered"][0].stats["strategy"] == "layered"
         for n in (1, 129, 20001):
             x = synth.config5_inputs(n, 31, num_features=sh["num_features"])
             x[::7, ::5] = np.nan
             x[3 % n, :] = np.nan
-            got = plan.execute_host(x)
             want = oracle_eval(q, x, True)
-            assert max_rel_err(got, want) <= REL_TOL_F32, (sh, n)
-            assert max_rel_err(interp.execute_host(x), want) <= REL_TOL_F32, (sh, n)
-        plan.close()
-        interp.close()
-        os.remove(plan_path)
-        os.remove(ip_path)
+            for mode, (plan, _) in plans.items():
+                err = max_rel_err(plan.execute_host(x), want)
+                assert err <= REL_TOL_F32, (sh, n, mode, err)
+        for plan, path in plans.values():
+            plan.close()
+            os.remove(path)
     # a model that is not layered is refused by the layered strategy
     name, spn, inputs, log_space, marginal = small_configs()[2]
     q = write_query(spn, marginal, directory=str(tmp_path))
