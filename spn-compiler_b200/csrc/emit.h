@@ -15,6 +15,7 @@ struct EmitOptions {
                            // on the same stretch of the instruction stream
   int gaussForm = 1;       // 1: fma(d, d, c1/c2) * c2 (three instructions); 0: fma(d*d, c2, c1)
   int chunkNodes = 2000;   // DAG nodes per generated function (0: one function)
+  int groupTiles = 0;      // chunked kernels: tiles a chunk runs on back to back (0 or 1: each tile runs all chunks)
   bool useMax3 = true;     // three-input max.f32 (needs a JIT that knows PTX ISA 8.8)
   int smemTableLimit = 64 * 1024;  // shared-memory window for leaf tables; larger tables are streamed through it
 };
@@ -26,7 +27,7 @@ struct EmitInfo {
   size_t dynamicSmemBytes = 0;
   bool tablesInSmem = false;
   size_t tableEntries = 0;
-  int scratchSlots = 0;     // values per sample that cross chunk boundaries through global scratch memory
+  int scratchSlots = 0;     // scratch values per CTA thread: cross-chunk values x tiles per group
 };
 
 std::string emitCuda(const Plan& plan, const EmitOptions& opt, EmitInfo* info);

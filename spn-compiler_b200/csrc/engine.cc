@@ -176,6 +176,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-gauss-form") o.gaussForm = std::atoi(v.c_str());
     else if (k == "spnb-table-window") o.tableWindow = std::atoi(v.c_str());
     else if (k == "spnb-chunk-nodes") o.chunkNodes = std::atoi(v.c_str());
+    else if (k == "spnb-group-tiles") o.groupTiles = std::atoi(v.c_str());
     else if (k == "spnb-interp-slots") o.interpSlots = std::atoi(v.c_str());
     else if (k == "spnb-mma-split") o.mmaSplit = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
@@ -225,6 +226,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     eo.syncEvery = opt.syncEvery;
     eo.gaussForm = opt.gaussForm;
     if (opt.chunkNodes >= 0) eo.chunkNodes = opt.chunkNodes;
+    eo.groupTiles = opt.groupTiles;
     if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
     eo.useMax3 = jitVersion() >= 1209;
     source = emitCuda(plan, eo, &ei);

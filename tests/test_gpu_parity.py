@@ -89,16 +89,17 @@ def test_chunked_kernels_pass_values_through_scratch(capi, tmp_path):
     for idx in (1, 2, 3, 4):
         name, spn, inputs, log_space, marginal = small_configs()[idx]
         q = write_query(spn, marginal, directory=str(tmp_path))
-        plan_path, _ = capi.compile_query(q, _opts(log_space, spnb_kernel="unrolled", spnb_chunk_nodes=97,
-                                                   spnb_table_window=2048))
-        plan = capi.Plan(plan_path)
-        assert plan.stats["scratch_slots"] > 0 and "st.global" in plan.source
-        for n in (1, 1025, 300001):
-            x = inputs(n)
-            err = max_rel_err(plan.execute_host(x), oracle_eval(q, x, log_space))
-            assert err <= REL_TOL_F32, (name, n, err)
-        plan.close()
-        os.remove(plan_path)
+        for group in (1, 3):   # 3: every chunk runs on three tiles in a row, each with its own scratch slice
+            plan_path, _ = capi.compile_query(q, _opts(log_space, spnb_kernel="unrolled", spnb_chunk_nodes=97,
+                                                       spnb_table_window=2048, spnb_group_tiles=group))
+            plan = capi.Plan(plan_path)
+            assert plan.stats["scratch_slots"] > 0 and "st.global" in plan.source
+            for n in (1, 1025, 300001):
+                x = inputs(n)
+                err = max_rel_err(plan.execute_host(x), oracle_eval(q, x, log_space))
+                assert err <= REL_TOL_F32, (name, n, group, err)
+            plan.close()
+            os.remove(plan_path)
 
 
 def test_interpreter_spills_values_to_scratch(capi, tmp_path):
