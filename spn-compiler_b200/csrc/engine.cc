@@ -166,7 +166,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "graph-stats-file") o.statsFile = v;
     else if (k == "optLevel") o.optLevel = std::atoi(v.c_str());
     else if (k == "spnb-kernel") {
-      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar") fail("Unknown value '" + v + "' for option spnb-kernel");
+      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar" && v != "layered-tc5") fail("Unknown value '" + v + "' for option spnb-kernel");
       o.kernelMode = v;
     } else if (k == "spnb-tile") o.tile = std::atoi(v.c_str());
     else if (k == "spnb-min-blocks") o.minBlocks = std::atoi(v.c_str());
@@ -198,7 +198,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   Strategy strat;
   const int64_t size = plan.stats.nodes + plan.stats.sumEdges + plan.stats.productEdges;
   LayeredPlan layered;
-  if (opt.kernelMode == "layered" || opt.kernelMode == "layered-scalar") {
+  if (opt.kernelMode == "layered" || opt.kernelMode == "layered-scalar" || opt.kernelMode == "layered-tc5") {
     if (!opt.logSpace || !recogniseLayers(plan.dag, &layered)) fail("spnb-kernel=layered needs a log-space query whose DAG is a layered (RAT-SPN-style) region graph");
     strat = kLayered;
   } else if (opt.kernelMode == "unrolled") strat = kUnrolled;
@@ -309,6 +309,8 @@ struct Engine::DeviceState {
   void* dFrags = nullptr;
   void* dScales = nullptr;
   bool useMma = false;
+  bool useTc5 = false;
+  int* dStatus = nullptr;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
   // because launches on different streams may overlap on the GPU
   size_t scratchBytes = 0;
@@ -347,6 +349,7 @@ struct Engine::DeviceState {
     if (dMma) cudaFree(dMma);
     if (dFrags) cudaFree(dFrags);
     if (dScales) cudaFree(dScales);
+    if (dStatus) cudaFree(dStatus);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -383,6 +386,7 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->interpSlotsCap_ = opt.interpSlots;
   e->layeredScalar_ = opt.kernelMode == "layered-scalar";
   e->mmaSplit_ = opt.mmaSplit != 0;
+  e->layeredTc5_ = opt.kernelMode == "layered-tc5";
   e->meta_.kernelName = e->model_.name;
   e->meta_.batchSize = (uint32_t)std::max(e->model_.batchSize, 0);
   e->meta_.numFeatures = (uint32_t)e->model_.numFeatures;
@@ -488,6 +492,25 @@ Engine::DeviceState& Engine::state(int device) {
           std::memcpy(&bits, &h, 2);
           return bits;
         };
+        if (layeredTc5_) {
+          // tcgen05 operand B: per k-step a 32 x 16 block, K-major core matrices [k-half][n-group][n % 8][8 halves]
+          mma[i].numTiles = 4;
+          for (int ks = 0; ks < 64; ++ks)
+            for (int kh = 0; kh < 2; ++kh)
+              for (int nrow = 0; nrow < 32; ++nrow) {
+                const int kk = 16 * ks + 8 * kh;
+                uint2 lo, hi;
+                lo.x = h16(nrow, kk + 0, false) | (h16(nrow, kk + 1, false) << 16);
+                lo.y = h16(nrow, kk + 2, false) | (h16(nrow, kk + 3, false) << 16);
+                hi.x = h16(nrow, kk + 4, false) | (h16(nrow, kk + 5, false) << 16);
+                hi.y = h16(nrow, kk + 6, false) | (h16(nrow, kk + 7, false) << 16);
+                frags.push_back(lo);
+                frags.push_back(hi);
+              }
+          while (scales.size() < (size_t)mma[i].scaleOffset + 32) scales.push_back(-INFINITY);
+          anyMma = true;
+          continue;
+        }
         for (int ks = 0; ks < 64; ++ks)
           for (int t = 0; t < nt; ++t)
             for (int lane = 0; lane < 32; ++lane) {
@@ -511,6 +534,20 @@ Engine::DeviceState& Engine::state(int device) {
       st->la.scales = (const float*)st->dScales;
       st->la.split = mmaSplit_ ? 1 : 0;
       st->useMma = true;
+      if (layeredTc5_) {
+        st->useTc5 = true;
+        CUDA_OK(cudaMalloc(&st->dStatus, sizeof(int)));
+        CUDA_OK(cudaMemset(st->dStatus, 0, sizeof(int)));
+        st->block = 128;
+        st->smem = layeredTc5SmemBytes(st->la);
+        if (st->smem > (size_t)prop.sharedMemPerBlockOptin) fail("Layered tcgen05 kernel: region stack too deep for shared memory");
+        int perSM5 = 0;
+        CUDA_OK(layeredTc5Occupancy(st->smem, &perSM5));
+        if (perSM5 < 1) fail("Layered tcgen05 kernel does not fit on one SM");
+        st->grid = perSM5 * st->smCount;
+        auto ins5 = dev_.emplace(device, std::move(st));
+        return *ins5.first->second;
+      }
       st->block = 256;
       st->smem = layeredMmaSmemBytes(st->la);
       if (st->smem > (size_t)prop.sharedMemPerBlockOptin) fail("Layered tensor-core kernel: region stack too deep for shared memory");
@@ -611,7 +648,10 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
   } else if (strategy_ == kLayered) {
-    if (st.useMma) CUDA_OK(layeredMmaLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.smem, stream));
+    if (st.useTc5) {
+      if (dtypeCode(plan_.ftype) != DT_F32 && dtypeCode(plan_.ftype) != DT_F64) fail("The tcgen05 layered kernel takes floating inputs only");
+      CUDA_OK(layeredTc5Launch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.smem, st.dStatus, stream));
+    } else if (st.useMma) CUDA_OK(layeredMmaLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.smem, stream));
     else CUDA_OK(layeredLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
   } else {
     InterpArgs ia = st.ia;
@@ -779,6 +819,14 @@ void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, fl
     CUDA_OK(cudaEventRecord(done[c], s));
   }
   drain(nChunks);
+  if (st.dStatus) {
+    int flag = 0;
+    CUDA_OK(cudaMemcpy(&flag, st.dStatus, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) {
+      cudaMemset(st.dStatus, 0, sizeof(int));
+      fail("tcgen05 layered kernel: a bounded wait on a tensor-core barrier gave up; results are incomplete");
+    }
+  }
   float total = 0.f;
   for (size_t c = 0; c < nChunks; ++c) {
     float ms = 0.f;

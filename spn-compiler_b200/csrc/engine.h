@@ -86,6 +86,7 @@ class Engine {
   int interpSlotsCap_ = 0;
   bool layeredScalar_ = false;
   bool mmaSplit_ = true;
+  bool layeredTc5_ = false;
   std::string source_;
   std::vector<char> cubin_;
   std::string statsJson_;

@@ -50,4 +50,12 @@ cudaError_t layeredMmaLaunch(const LayeredArgs& a, int dtypeCode, const void* in
                              size_t smem, cudaStream_t stream);
 cudaError_t layeredMmaOccupancy(size_t smem, int* blocksPerSM);
 
+// tcgen05 / TMEM version: CTAs of 128 samples; LayeredArgs::frags holds, per full-width region, 64 k-step
+// blocks of 1 KB in the K-major non-swizzled core-matrix layout [k-half][n-group][n % 8][8 halves]
+// (MmaRegionDev::fragOffset counts 8-byte units).  *status is set to 1 if a bounded wait gave up.
+size_t layeredTc5SmemBytes(const LayeredArgs& a);
+cudaError_t layeredTc5Launch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid,
+                             size_t smem, int* status, cudaStream_t stream);
+cudaError_t layeredTc5Occupancy(size_t smem, int* blocksPerSM);
+
 }  // namespace spnb
