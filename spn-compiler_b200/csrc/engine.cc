@@ -310,6 +310,7 @@ struct Engine::DeviceState {
   void* dScales = nullptr;
   bool useMma = false;
   bool useTc5 = false;
+  size_t layeredChunkRows = 0;
   int* dStatus = nullptr;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
   // because launches on different streams may overlap on the GPU
@@ -545,6 +546,8 @@ Engine::DeviceState& Engine::state(int device) {
         CUDA_OK(layeredTc5Occupancy(st->smem, &perSM5));
         if (perSM5 < 1) fail("Layered tcgen05 kernel does not fit on one SM");
         st->grid = perSM5 * st->smCount;
+        st->layeredChunkRows = 512 * 1024;
+        st->scratchBytes = st->layeredChunkRows * (size_t)p.features.size() * 4;
         auto ins5 = dev_.emplace(device, std::move(st));
         return *ins5.first->second;
       }
@@ -565,6 +568,8 @@ Engine::DeviceState& Engine::state(int device) {
       if (perSM < 1) fail("Layered kernel does not fit on one SM");
       st->grid = perSM * st->smCount;
     }
+    st->layeredChunkRows = 512 * 1024;
+    st->scratchBytes = st->layeredChunkRows * (size_t)p.features.size() * 4;
   } else {
     std::vector<int4> meta(p.features.size());
     for (size_t f = 0; f < meta.size(); ++f)
@@ -648,11 +653,25 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
   } else if (strategy_ == kLayered) {
-    if (st.useTc5) {
-      if (dtypeCode(plan_.ftype) != DT_F32 && dtypeCode(plan_.ftype) != DT_F64) fail("The tcgen05 layered kernel takes floating inputs only");
-      CUDA_OK(layeredTc5Launch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.smem, st.dStatus, stream));
-    } else if (st.useMma) CUDA_OK(layeredMmaLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.smem, stream));
-    else CUDA_OK(layeredLaunch(st.la, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
+    // The batch is first copied into a feature-major float matrix in scratch memory (one area per stream),
+    // at most kLayeredChunk samples at a time; the layered kernels then read it coalesced.
+    const size_t kLayeredChunk = st.layeredChunkRows;
+    float* xt = (float*)scratchFor(st, stream);
+    const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature;
+    for (size_t r0 = 0; r0 < n; r0 += kLayeredChunk) {
+      const size_t rows = std::min(kLayeredChunk, n - r0);
+      const size_t ld = (rows + 255) / 256 * 256;
+      const void* src = (const char*)dIn + r0 * rowBytes;
+      float* dst = (float*)dOut + r0;
+      CUDA_OK(transposeInputs(dtypeCode(plan_.ftype), src, xt, rows, (int)meta_.numFeatures, ld, stream));
+      LayeredArgs la = st.la;
+      la.xtLd = (long long)ld;
+      const size_t tilesC = (rows + (size_t)st.block - 1) / (size_t)st.block;
+      const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);
+      if (st.useTc5) CUDA_OK(layeredTc5Launch(la, DT_F32, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
+      else if (st.useMma) CUDA_OK(layeredMmaLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, stream));
+      else CUDA_OK(layeredLaunch(la, DT_F32, xt, dst, rows, gridC, st.block, st.smem, stream));
+    }
   } else {
     InterpArgs ia = st.ia;
     ia.scratch = (float*)scratchFor(st, stream);

@@ -52,7 +52,9 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
   for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const unsigned long long row = tile * T + tid;
     const bool live = row < n;
-    const in_t* __restrict__ x = in + (live ? row : 0) * F;
+    const in_t* __restrict__ x = in + (a.xtLd ? 0 : (live ? row : 0) * F);
+    // feature-major float copy of the batch (see transposeInputs): consecutive samples are consecutive floats
+    const float* __restrict__ xT = reinterpret_cast<const float*>(in) + (live ? row : 0);
     int sp = 0;
     float rootM = __int_as_float(0xff800000), rootS = 0.f;
     for (int si = 0; si < a.numSteps; ++si) {
@@ -65,25 +67,40 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
         float acc[KMAX];
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) acc[k] = 0.f;
-        for (int f = 0; f < s.numFeatures; ++f) {
-          float xv = (float)x[__ldg(a.features + s.featOffset + f)];
-          float m = 1.f;
-          if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
-          const float4* p = pbuf + f * s.width;
-          if (s.width == KMAX) {   // full-width region: no guards, the 32 chains interleave freely
+        // inputs are fetched eight features ahead: the loads of one batch are independent, so their latency
+        // overlaps instead of sitting in front of every feature's 32 updates
+        for (int f0 = 0; f0 < s.numFeatures; f0 += 8) {
+          float xpre[8];
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-              const float4 q = p[k];
-              const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
-              acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
-            }
-          } else {
+          for (int u = 0; u < 8; ++u) {
+            const int fu = f0 + u < s.numFeatures ? f0 + u : s.numFeatures - 1;
+            const int col = __ldg(a.features + s.featOffset + fu);
+            xpre[u] = a.xtLd ? xT[(size_t)col * a.xtLd] : (float)x[col];
+          }
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-              if (k < s.width) {
-                const float4 q = p[k];
-                const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
-                acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+          for (int u = 0; u < 8; ++u) {
+            const int f = f0 + u;
+            if (f < s.numFeatures) {
+              float xv = xpre[u];
+              float m = 1.f;
+              if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
+              const float4* p = pbuf + f * s.width;
+              if (s.width == KMAX) {   // full-width region: no guards, the 32 chains interleave freely
+    #pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                  const float4 q = p[k];
+                  const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                  acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+                }
+              } else {
+    #pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                  if (k < s.width) {
+                    const float4 q = p[k];
+                    const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                    acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+                  }
+                }
               }
             }
           }
@@ -206,6 +223,49 @@ cudaError_t launchT(const LayeredArgs& a, const void* in, float* out, size_t n, 
 }
 
 }  // namespace
+
+namespace {
+template <typename in_t>
+__global__ void transposeKernel(const in_t* __restrict__ in, float* __restrict__ xt, unsigned long long n, int F,
+                                unsigned long long ld) {
+  __shared__ float tileBuf[32][33];
+  const unsigned long long s0 = (unsigned long long)blockIdx.x * 32;
+  const int f0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const unsigned long long srow = s0 + r;
+    const int f = f0 + threadIdx.x;
+    tileBuf[r][threadIdx.x] = (srow < n && f < F) ? (float)in[srow * F + f] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int f = f0 + r;
+    const unsigned long long srow = s0 + threadIdx.x;
+    if (f < F && srow < ld) xt[(unsigned long long)f * ld + srow] = tileBuf[threadIdx.x][r];
+  }
+}
+template <typename in_t>
+cudaError_t transposeT(const void* in, float* xt, size_t n, int F, size_t ld, cudaStream_t stream) {
+  dim3 grid((unsigned)((ld + 31) / 32), (unsigned)((F + 31) / 32)), block(32, 8);
+  transposeKernel<in_t><<<grid, block, 0, stream>>>(static_cast<const in_t*>(in), xt, n, F, ld);
+  return cudaGetLastError();
+}
+}  // namespace
+
+cudaError_t transposeInputs(int dtypeCode, const void* in, float* xt, size_t n, int F, size_t ld, cudaStream_t stream) {
+  switch (dtypeCode) {
+    case DT_U8: return transposeT<uint8_t>(in, xt, n, F, ld, stream);
+    case DT_I8: return transposeT<int8_t>(in, xt, n, F, ld, stream);
+    case DT_U16: return transposeT<uint16_t>(in, xt, n, F, ld, stream);
+    case DT_I16: return transposeT<int16_t>(in, xt, n, F, ld, stream);
+    case DT_U32: return transposeT<uint32_t>(in, xt, n, F, ld, stream);
+    case DT_I32: return transposeT<int32_t>(in, xt, n, F, ld, stream);
+    case DT_U64: return transposeT<uint64_t>(in, xt, n, F, ld, stream);
+    case DT_I64: return transposeT<int64_t>(in, xt, n, F, ld, stream);
+    case DT_F32: return transposeT<float>(in, xt, n, F, ld, stream);
+    case DT_F64: return transposeT<double>(in, xt, n, F, ld, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
 
 size_t layeredSmemBytes(const LayeredArgs& a, int tile) {
   return ((size_t)a.maxDepth * KMAX * tile + KMAX * KMAX) * 4 + (size_t)a.maxLeafFeatures * KMAX * 16;

@@ -31,6 +31,7 @@ struct LayeredArgs {
   int maxDepth;
   int maxLeafFeatures;
   int marginal;
+  long long xtLd;          // > 0: `in` is a feature-major float matrix [numInputFeatures][xtLd] made by transposeInputs
   // tensor-core path (null / 0 when absent)
   const MmaRegionDev* mma;     // per step; fragOffset < 0: the step has no fragments (scalar code runs it)
   const uint2* frags;
@@ -39,6 +40,12 @@ struct LayeredArgs {
 };
 
 size_t layeredSmemBytes(const LayeredArgs& a, int tile);
+
+// Feature-major float copy of a row-major batch: xt[f * ld + s] = (float)in[s * F + f].  The layered kernels
+// read one feature of many consecutive samples at a time; from the row-major layout every such read would
+// touch a different 32-byte sector per sample.
+cudaError_t transposeInputs(int dtypeCode, const void* in, float* xt, size_t n, int numFeatures, size_t ld,
+                            cudaStream_t stream);
 cudaError_t layeredLaunch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
                           size_t smem, cudaStream_t stream);
 cudaError_t layeredOccupancy(int tile, size_t smem, int* blocksPerSM);

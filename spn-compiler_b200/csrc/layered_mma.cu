@@ -83,7 +83,9 @@ __global__ void __launch_bounds__(TM, 1) layeredMmaKernel(LayeredArgs a, const i
   for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const unsigned long long row = tile * TM + tid;
     const bool live = row < n;
-    const in_t* __restrict__ x = in + (live ? row : 0) * F;
+    const in_t* __restrict__ x = in + (a.xtLd ? 0 : (live ? row : 0) * F);
+    // feature-major float copy of the batch (see transposeInputs): consecutive samples are consecutive floats
+    const float* __restrict__ xT = reinterpret_cast<const float*>(in) + (live ? row : 0);
     int sp = 0;
     rootM[tid] = NEG;
     rootS[tid] = 0.f;
@@ -97,25 +99,40 @@ __global__ void __launch_bounds__(TM, 1) layeredMmaKernel(LayeredArgs a, const i
         float acc[KMAX];
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) acc[k] = 0.f;
-        for (int f = 0; f < s.numFeatures; ++f) {
-          float xv = (float)x[__ldg(a.features + s.featOffset + f)];
-          float m = 1.f;
-          if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
-          const float4* p = pbuf + f * s.width;
-          if (s.width == KMAX) {
+        // inputs are fetched eight features ahead: the loads of one batch are independent, so their latency
+        // overlaps instead of sitting in front of every feature's 32 updates
+        for (int f0 = 0; f0 < s.numFeatures; f0 += 8) {
+          float xpre[8];
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-              const float4 q = p[k];
-              const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
-              acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
-            }
-          } else {
+          for (int u = 0; u < 8; ++u) {
+            const int fu = f0 + u < s.numFeatures ? f0 + u : s.numFeatures - 1;
+            const int col = __ldg(a.features + s.featOffset + fu);
+            xpre[u] = a.xtLd ? xT[(size_t)col * a.xtLd] : (float)x[col];
+          }
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-              if (k < s.width) {
-                const float4 q = p[k];
-                const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
-                acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+          for (int u = 0; u < 8; ++u) {
+            const int f = f0 + u;
+            if (f < s.numFeatures) {
+              float xv = xpre[u];
+              float m = 1.f;
+              if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
+              const float4* p = pbuf + f * s.width;
+              if (s.width == KMAX) {
+    #pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                  const float4 q = p[k];
+                  const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                  acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+                }
+              } else {
+    #pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                  if (k < s.width) {
+                    const float4 q = p[k];
+                    const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                    acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+                  }
+                }
               }
             }
           }

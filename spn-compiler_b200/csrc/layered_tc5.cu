@@ -36,7 +36,7 @@ namespace {
 
 constexpr int KMAX = 32;
 constexpr int TS = 128;            // samples (threads) per CTA = MMA M
-constexpr int STAGE_KSTEPS = 8;    // k-steps of 16 per stage
+constexpr int STAGE_KSTEPS = 2;    // k-steps of 16 per stage (small stages: two CTAs fit on one SM)
 constexpr int A_KSTEP_BYTES = TS * 16 * 2;          // 4096: [k-half 2][row group 16][row 8][8 halves]
 constexpr int A_STAGE_BYTES = STAGE_KSTEPS * A_KSTEP_BYTES;   // 32 KB
 constexpr int B_KSTEP_BYTES = KMAX * 16 * 2;        // 1024: [k-half 2][n group 4][n 8][8 halves]
@@ -88,9 +88,9 @@ __device__ __forceinline__ unsigned long long smemDesc(unsigned addr, unsigned l
 }
 
 // shared memory: [stack float x maxDepth*32*128][mab, rootM, rootS float x 128][bars 8 x u64][tmem addr]
-//                [A stages 2 x 32 KB][B stages 2 x 8 KB]   (leaf parameters / scalar weight row overlay A)
+//                [A stages 2 x 8 KB][B stages 2 x 2 KB]   (the scalar path's weight row overlays them)
 template <typename in_t, bool MARGINAL>
-__global__ void __launch_bounds__(TS, 1) layeredTc5Kernel(LayeredArgs a, const in_t* __restrict__ in,
+__global__ void __launch_bounds__(TS, 2) layeredTc5Kernel(LayeredArgs a, const in_t* __restrict__ in,
                                                            float* __restrict__ out, unsigned long long n,
                                                            int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -106,7 +106,6 @@ __global__ void __launch_bounds__(TS, 1) layeredTc5Kernel(LayeredArgs a, const i
       (reinterpret_cast<uintptr_t>(tmemSlot + 4) + 127) & ~uintptr_t(127));
   unsigned char* bbuf = abuf + 2 * A_STAGE_BYTES;
   float* wbuf = reinterpret_cast<float*>(abuf);
-  float4* pbuf = reinterpret_cast<float4*>(abuf);
   const unsigned F = a.numInputFeatures;
   const float NEG = __int_as_float(0xff800000);
   const unsigned barFree0 = smemAddr(bars), barFree1 = smemAddr(bars + 1), barDone = smemAddr(bars + 2);
@@ -137,39 +136,55 @@ __global__ void __launch_bounds__(TS, 1) layeredTc5Kernel(LayeredArgs a, const i
   for (unsigned long long tile = blockIdx.x; tile < ntiles && !failed; tile += gridDim.x) {
     const unsigned long long row = tile * TS + tid;
     const bool live = row < n;
-    const in_t* __restrict__ x = in + (live ? row : 0) * F;
+    const in_t* __restrict__ x = in + (a.xtLd ? 0 : (live ? row : 0) * F);
+    // feature-major float copy of the batch (see transposeInputs): consecutive samples are consecutive floats
+    const float* __restrict__ xT = reinterpret_cast<const float*>(in) + (live ? row : 0);
     int sp = 0;
     rootM[tid] = NEG;
     rootS[tid] = 0.f;
     for (int si = 0; si < a.numSteps && !failed; ++si) {
       const LayerStepDev s = a.steps[si];
       if (s.op == kLeafRegion) {
-        const int cnt = s.numFeatures * s.width;
-        __syncthreads();
-        for (int i = tid; i < cnt; i += TS) pbuf[i] = a.quad[s.paramOffset + i];
-        __syncthreads();
+        // leaf parameters are read straight from global memory: every thread reads the same address
+        // (one broadcast transaction, L1-resident), and no shared memory has to be set aside for them
+        const float4* __restrict__ pbuf = a.quad + s.paramOffset;
         float acc[KMAX];
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) acc[k] = 0.f;
-        for (int f = 0; f < s.numFeatures; ++f) {
-          float xv = (float)x[__ldg(a.features + s.featOffset + f)];
-          float m = 1.f;
-          if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
-          const float4* p = pbuf + f * s.width;
-          if (s.width == KMAX) {
+        // inputs are fetched eight features ahead: the loads of one batch are independent, so their latency
+        // overlaps instead of sitting in front of every feature's 32 updates
+        for (int f0 = 0; f0 < s.numFeatures; f0 += 8) {
+          float xpre[8];
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-              const float4 q = p[k];
-              const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
-              acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
-            }
-          } else {
+          for (int u = 0; u < 8; ++u) {
+            const int fu = f0 + u < s.numFeatures ? f0 + u : s.numFeatures - 1;
+            const int col = __ldg(a.features + s.featOffset + fu);
+            xpre[u] = a.xtLd ? xT[(size_t)col * a.xtLd] : (float)x[col];
+          }
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-              if (k < s.width) {
-                const float4 q = p[k];
-                const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
-                acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+          for (int u = 0; u < 8; ++u) {
+            const int f = f0 + u;
+            if (f < s.numFeatures) {
+              float xv = xpre[u];
+              float m = 1.f;
+              if (MARGINAL && xv != xv) { xv = 0.f; m = 0.f; }
+              const float4* p = pbuf + f * s.width;
+              if (s.width == KMAX) {
+    #pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                  const float4 q = __ldg(p + k);
+                  const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                  acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+                }
+              } else {
+    #pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                  if (k < s.width) {
+                    const float4 q = __ldg(p + k);
+                    const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                    acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
+                  }
+                }
               }
             }
           }
@@ -217,9 +232,10 @@ __global__ void __launch_bounds__(TS, 1) layeredTc5Kernel(LayeredArgs a, const i
         const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(a.frags) + mr.fragOffset * 8;
         __syncthreads();   // leaf parameters / scalar weights that overlay the A stages are no longer read
         const unsigned rowOff = (tid >> 3) * 128 + (tid & 7) * 16;   // this row inside one k-half block
-        constexpr int NSTAGES = (KMAX * KMAX / 16) / STAGE_KSTEPS;   // 8
-#pragma unroll 1
-        for (int st = 0; st < NSTAGES && !failed; ++st) {
+        constexpr int NSTAGES = (KMAX * KMAX / 16) / STAGE_KSTEPS;
+#pragma unroll
+        for (int st = 0; st < NSTAGES; ++st) {
+          if (failed) break;
           const int b = st & 1;
           // the tensor core must be done with this buffer (its MMAs of two stages ago)
           if (b == 0 ? used0 : used1) {
@@ -234,19 +250,17 @@ __global__ void __launch_bounds__(TS, 1) layeredTc5Kernel(LayeredArgs a, const i
             for (int o = tid * 16; o < B_STAGE_BYTES; o += TS * 16) cpAsync16(dst + o, src + o);
             asm volatile("cp.async.commit_group;" ::: "memory");
           }
-          // outer products of the stage: k-step ks covers i = 4 st + ks / 2, j = 16 (ks & 1) .. + 15
+          // outer products of the stage: k-step ks covers i = (st * STAGE_KSTEPS + ks) / 2, j = 16 (ks & 1) .. + 15
           unsigned char* adst = abuf + b * A_STAGE_BYTES + rowOff;
 #pragma unroll
           for (int ks = 0; ks < STAGE_KSTEPS; ++ks) {
-            const int ii = ks >> 1, h = ks & 1;
+            const int h = ks & 1;
+            // ea[i] with i = (st * STAGE_KSTEPS + ks) / 2, picked with selects so that ea stays in registers
+            const int iWanted = (st * STAGE_KSTEPS + ks) >> 1;
             float e = 0.f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              if (q == ii) {
-#pragma unroll
-                for (int c = 0; c < KMAX / 4; ++c)
-                  if (c == (st & 7)) e = ea[4 * c + q];   // ea[4 st + ii], register-indexed without local memory
-              }
+            for (int c = 0; c < KMAX; ++c)
+              if (c == iWanted) e = ea[c];
             uint4 lo, hi;
             lo.x = packHalf2(e * eb[16 * h + 0], e * eb[16 * h + 1]);
             lo.y = packHalf2(e * eb[16 * h + 2], e * eb[16 * h + 3]);
@@ -367,8 +381,8 @@ cudaError_t launchT(const LayeredArgs& a, const void* in, float* out, size_t n, 
 size_t layeredTc5SmemBytes(const LayeredArgs& a) {
   size_t fixed = ((size_t)a.maxDepth * KMAX * TS + 3 * TS) * 4 + 8 * 8 + 16 + 128;
   size_t stages = 2 * (size_t)A_STAGE_BYTES + 2 * (size_t)B_STAGE_BYTES;
-  size_t leaf = (size_t)a.maxLeafFeatures * KMAX * 16;
-  return fixed + (stages > leaf ? stages : leaf);
+  size_t scalarRow = (size_t)KMAX * KMAX * 4;
+  return fixed + (stages > scalarRow ? stages : scalarRow);
 }
 
 cudaError_t layeredTc5Occupancy(size_t smem, int* blocksPerSM) {
