@@ -166,7 +166,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "graph-stats-file") o.statsFile = v;
     else if (k == "optLevel") o.optLevel = std::atoi(v.c_str());
     else if (k == "spnb-kernel") {
-      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar" && v != "layered-tc5") fail("Unknown value '" + v + "' for option spnb-kernel");
+      if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar" && v != "layered-mma") fail("Unknown value '" + v + "' for option spnb-kernel");
       o.kernelMode = v;
     } else if (k == "spnb-tile") o.tile = std::atoi(v.c_str());
     else if (k == "spnb-min-blocks") o.minBlocks = std::atoi(v.c_str());
@@ -179,6 +179,10 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-group-tiles") o.groupTiles = std::atoi(v.c_str());
     else if (k == "spnb-interp-slots") o.interpSlots = std::atoi(v.c_str());
     else if (k == "spnb-mma-split") o.mmaSplit = std::atoi(v.c_str());
+    else if (k == "spnb-tc-warpgroups") {
+      o.tcWarpgroups = std::atoi(v.c_str());
+      if (o.tcWarpgroups != 1 && o.tcWarpgroups != 2 && o.tcWarpgroups != 4) fail("spnb-tc-warpgroups must be 1, 2 or 4");
+    }
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -198,7 +202,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   Strategy strat;
   const int64_t size = plan.stats.nodes + plan.stats.sumEdges + plan.stats.productEdges;
   LayeredPlan layered;
-  if (opt.kernelMode == "layered" || opt.kernelMode == "layered-scalar" || opt.kernelMode == "layered-tc5") {
+  if (opt.kernelMode == "layered" || opt.kernelMode == "layered-scalar" || opt.kernelMode == "layered-mma") {
     if (!opt.logSpace || !recogniseLayers(plan.dag, &layered)) fail("spnb-kernel=layered needs a log-space query whose DAG is a layered (RAT-SPN-style) region graph");
     strat = kLayered;
   } else if (opt.kernelMode == "unrolled") strat = kUnrolled;
@@ -309,7 +313,9 @@ struct Engine::DeviceState {
   void* dFrags = nullptr;
   void* dScales = nullptr;
   bool useMma = false;
-  bool useTc5 = false;
+  bool useTcf = false;
+  void* dCentres = nullptr;
+  void* dLeafCols = nullptr;
   size_t layeredChunkRows = 0;
   int* dStatus = nullptr;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
@@ -351,6 +357,8 @@ struct Engine::DeviceState {
     if (dFrags) cudaFree(dFrags);
     if (dScales) cudaFree(dScales);
     if (dStatus) cudaFree(dStatus);
+    if (dCentres) cudaFree(dCentres);
+    if (dLeafCols) cudaFree(dLeafCols);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -387,7 +395,9 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->interpSlotsCap_ = opt.interpSlots;
   e->layeredScalar_ = opt.kernelMode == "layered-scalar";
   e->mmaSplit_ = opt.mmaSplit != 0;
-  e->layeredTc5_ = opt.kernelMode == "layered-tc5";
+  e->tcWarpgroups_ = opt.tcWarpgroups;
+  // layered models run on the tensor-memory kernel unless another layered kernel is asked for by name
+  e->layeredTcf_ = opt.kernelMode != "layered-scalar" && opt.kernelMode != "layered-mma";
   e->meta_.kernelName = e->model_.name;
   e->meta_.batchSize = (uint32_t)std::max(e->model_.batchSize, 0);
   e->meta_.numFeatures = (uint32_t)e->model_.numFeatures;
@@ -469,7 +479,111 @@ Engine::DeviceState& Engine::state(int device) {
     std::vector<uint2> frags;
     std::vector<float> scales;
     bool anyMma = false;
-    if (!layeredScalar_) {
+    std::vector<float> centres(lp.features.size(), 0.f);
+    std::vector<int> leafCols;        // flat list of leaf stages (eight slots each), see LayeredArgs::leafCols
+    std::vector<float> leafCentres;
+    auto halfBits = [](float v, bool residue) -> unsigned {
+      __half h = __float2half_rn(v);
+      if (residue) h = __float2half_rn(v - __half2float(h));
+      unsigned short bits;
+      std::memcpy(&bits, &h, 2);
+      return bits;
+    };
+    if (layeredTcf_) {
+      // Factorised tensor-memory kernel (layered_tcf.cu).  All blocks are in the K-major core-matrix layout
+      // [k-half][row group][row % 8][8 halves]; one row of a k-half is 16 bytes = two uint2.
+      for (size_t i = 0; i < steps.size(); ++i) {
+        const LayerStep& s = lp.steps[i];
+        if (s.width > 32) continue;
+        if (s.op == kLeafRegion) {
+          // per feature: centre = mean of the components' means; parameters re-expanded around it in double
+          const int F = s.numFeatures, K = s.width;
+          std::vector<double> ca((size_t)F * K), cb((size_t)F * K), cc((size_t)F * K);
+          bool ok = true;
+          for (int f = 0; f < F; ++f) {
+            double mean = 0.0;
+            int cnt = 0;
+            for (int k = 0; k < K; ++k) {
+              const float* q = lp.quad.data() + (s.paramOffset + (size_t)f * K + k) * 4;
+              if (q[0] != 0.f) { mean += -0.5 * (double)q[1] / (double)q[0]; ++cnt; }
+            }
+            const float m = cnt ? (float)(mean / cnt) : 0.f;
+            if (!std::isfinite(m)) ok = false;
+            centres[(size_t)s.featOffset + f] = m;
+            for (int k = 0; k < K; ++k) {
+              const float* q = lp.quad.data() + (s.paramOffset + (size_t)f * K + k) * 4;
+              const double A = q[0], B = q[1], C = q[2], M = m;
+              const size_t at = (size_t)f * K + k;
+              ca[at] = A;
+              cb[at] = 2.0 * A * M + B;
+              cc[at] = (A * M + B) * M + C;
+              for (double v : {ca[at], cb[at], cc[at]})
+                if (!(std::fabs(v) < 60000.0)) ok = false;
+            }
+          }
+          if (!ok) continue;   // parameters outside half-precision range: the kernel's FP32 loop runs the region
+          const int nst = (F + 7) / 8;
+          mma[i].fragOffset = (long long)frags.size();
+          mma[i].scaleOffset = (int)(leafCols.size() / 8);
+          mma[i].numTiles = nst;
+          for (int st = 0; st < (nst + 3) / 4 * 4; ++st)
+            for (int u = 0; u < 8; ++u) {
+              const int f = 8 * st + u;
+              leafCols.push_back(f < F ? lp.features[(size_t)s.featOffset + f] : 0);
+              leafCentres.push_back(f < F ? centres[(size_t)s.featOffset + f] : 0.f);
+            }
+          for (int st = 0; st < nst; ++st)
+            for (int ks = 0; ks < 4; ++ks)
+              for (int kh = 0; kh < 2; ++kh)
+                for (int k = 0; k < 32; ++k) {
+                  const int f = 8 * st + 2 * ks + kh;
+                  unsigned h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                  if (f < F && k < K) {
+                    const size_t at = (size_t)f * K + k;
+                    const float A = (float)ca[at], B = (float)cb[at], C = (float)cc[at];
+                    h[0] = halfBits(A, false); h[1] = h[0]; h[2] = halfBits(A, true);
+                    h[3] = halfBits(B, false); h[4] = h[3]; h[5] = halfBits(B, true);
+                    h[6] = halfBits(C, false); h[7] = halfBits(C, true);
+                  }
+                  frags.push_back(uint2{h[0] | (h[1] << 16), h[2] | (h[3] << 16)});
+                  frags.push_back(uint2{h[4] | (h[5] << 16), h[6] | (h[7] << 16)});
+                }
+          anyMma = true;
+          continue;
+        }
+        if (s.wa != 32 || s.wb != 32) continue;
+        // inner region: columns (k, i), blocks of 128 columns; per block four k-step chunks:
+        // value j 0..15, value j 16..31, residue j 0..15, residue j 16..31
+        const int nblk = (s.width * 32 + 127) / 128;
+        mma[i].fragOffset = (long long)frags.size();
+        mma[i].scaleOffset = (int)scales.size();
+        mma[i].numTiles = nblk;
+        const float* W = lp.weights.data() + s.paramOffset;
+        std::vector<float> inv(32, 0.f);
+        for (int k = 0; k < 32; ++k) {
+          float mx = 0.f;
+          if (k < s.width) for (int q = 0; q < 1024; ++q) mx = std::max(mx, W[(size_t)k * 1024 + q]);
+          inv[(size_t)k] = mx > 0.f ? 1.f / mx : 0.f;
+          scales.push_back(mx > 0.f ? std::log2(mx) : -INFINITY);
+        }
+        for (int nb = 0; nb < nblk; ++nb)
+          for (int chunk = 0; chunk < 4; ++chunk)
+            for (int kh = 0; kh < 2; ++kh)
+              for (int r = 0; r < 128; ++r) {
+                const int col = 128 * nb + r, k = col >> 5, ii = col & 31;
+                const int j0 = 16 * (chunk & 1) + 8 * kh;
+                unsigned h[8];
+                for (int q = 0; q < 8; ++q) {
+                  const float v = k < s.width ? W[(size_t)k * 1024 + ii * 32 + j0 + q] * inv[(size_t)k] : 0.f;
+                  h[q] = halfBits(v, chunk >= 2);
+                }
+                frags.push_back(uint2{h[0] | (h[1] << 16), h[2] | (h[3] << 16)});
+                frags.push_back(uint2{h[4] | (h[5] << 16), h[6] | (h[7] << 16)});
+              }
+        anyMma = true;
+      }
+    }
+    if (!layeredScalar_ && !layeredTcf_) {
       for (size_t i = 0; i < steps.size(); ++i) {
         const LayerStep& s = lp.steps[i];
         if (s.op == kLeafRegion || s.wa != 32 || s.wb != 32 || s.width > 32) continue;
@@ -493,25 +607,6 @@ Engine::DeviceState& Engine::state(int device) {
           std::memcpy(&bits, &h, 2);
           return bits;
         };
-        if (layeredTc5_) {
-          // tcgen05 operand B: per k-step a 32 x 16 block, K-major core matrices [k-half][n-group][n % 8][8 halves]
-          mma[i].numTiles = 4;
-          for (int ks = 0; ks < 64; ++ks)
-            for (int kh = 0; kh < 2; ++kh)
-              for (int nrow = 0; nrow < 32; ++nrow) {
-                const int kk = 16 * ks + 8 * kh;
-                uint2 lo, hi;
-                lo.x = h16(nrow, kk + 0, false) | (h16(nrow, kk + 1, false) << 16);
-                lo.y = h16(nrow, kk + 2, false) | (h16(nrow, kk + 3, false) << 16);
-                hi.x = h16(nrow, kk + 4, false) | (h16(nrow, kk + 5, false) << 16);
-                hi.y = h16(nrow, kk + 6, false) | (h16(nrow, kk + 7, false) << 16);
-                frags.push_back(lo);
-                frags.push_back(hi);
-              }
-          while (scales.size() < (size_t)mma[i].scaleOffset + 32) scales.push_back(-INFINITY);
-          anyMma = true;
-          continue;
-        }
         for (int ks = 0; ks < 64; ++ks)
           for (int t = 0; t < nt; ++t)
             for (int lane = 0; lane < 32; ++lane) {
@@ -526,6 +621,11 @@ Engine::DeviceState& Engine::state(int device) {
         anyMma = true;
       }
     }
+    if (layeredTcf_) {
+      anyMma = true;   // the kernel reads the per-step table for every step
+      if (frags.empty()) frags.push_back(uint2{0, 0});
+      if (scales.empty()) scales.push_back(0.f);
+    }
     if (anyMma) {
       st->dMma = upload(mma.data(), mma.size() * sizeof(MmaRegionDev));
       st->dFrags = upload(frags.data(), frags.size() * sizeof(uint2));
@@ -535,21 +635,25 @@ Engine::DeviceState& Engine::state(int device) {
       st->la.scales = (const float*)st->dScales;
       st->la.split = mmaSplit_ ? 1 : 0;
       st->useMma = true;
-      if (layeredTc5_) {
-        st->useTc5 = true;
+      if (layeredTcf_) {
+        st->useTcf = true;
+        st->la.numLeafStages = (int)(leafCols.size() / 8);
+        if (leafCols.empty()) { leafCols.assign(8, 0); leafCentres.assign(8, 0.f); }
+        st->dLeafCols = upload(leafCols.data(), leafCols.size() * 4);
+        st->dCentres = upload(leafCentres.data(), leafCentres.size() * 4);
+        st->la.leafCols = (const int*)st->dLeafCols;
+        st->la.leafCentres = (const float*)st->dCentres;
+        st->la.warpgroups = tcWarpgroups_;
         CUDA_OK(cudaMalloc(&st->dStatus, sizeof(int)));
         CUDA_OK(cudaMemset(st->dStatus, 0, sizeof(int)));
         st->block = 128;
-        st->smem = layeredTc5SmemBytes(st->la);
+        st->smem = layeredTcfSmemBytes(st->la);
         if (st->smem > (size_t)prop.sharedMemPerBlockOptin) fail("Layered tcgen05 kernel: region stack too deep for shared memory");
-        int perSM5 = 0;
-        CUDA_OK(layeredTc5Occupancy(st->smem, &perSM5));
-        if (perSM5 < 1) fail("Layered tcgen05 kernel does not fit on one SM");
-        st->grid = perSM5 * st->smCount;
+        st->grid = st->smCount;   // one CTA per SM: the kernel owns the SM's tensor memory
         st->layeredChunkRows = 512 * 1024;
         st->scratchBytes = st->layeredChunkRows * (size_t)p.features.size() * 4;
-        auto ins5 = dev_.emplace(device, std::move(st));
-        return *ins5.first->second;
+        auto insF = dev_.emplace(device, std::move(st));
+        return *insF.first->second;
       }
       st->block = 256;
       st->smem = layeredMmaSmemBytes(st->la);
@@ -668,7 +772,7 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
       la.xtLd = (long long)ld;
       const size_t tilesC = (rows + (size_t)st.block - 1) / (size_t)st.block;
       const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);
-      if (st.useTc5) CUDA_OK(layeredTc5Launch(la, DT_F32, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
+      if (st.useTcf) CUDA_OK(layeredTcfLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
       else if (st.useMma) CUDA_OK(layeredMmaLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, stream));
       else CUDA_OK(layeredLaunch(la, DT_F32, xt, dst, rows, gridC, st.block, st.smem, stream));
     }

@@ -30,7 +30,7 @@ struct Options {
   bool collectStats = false;   // "collect-graph-stats"
   std::string statsFile = "/tmp/stats.json";
   int optLevel = 3;            // "optLevel"
-  std::string kernelMode = "auto";  // "spnb-kernel": auto | unrolled | interp
+  std::string kernelMode = "auto";  // "spnb-kernel": auto | unrolled | interp | layered | layered-mma | layered-scalar
   int tile = 0;                // "spnb-tile": threads per CTA (0 = default)
   int minBlocks = 0;           // "spnb-min-blocks": __launch_bounds__ hint of the generated kernel
   int syncEvery = 0;           // "spnb-sync-every"
@@ -39,6 +39,7 @@ struct Options {
   int gaussForm = 1;           // "spnb-gauss-form"
   int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
   int mmaSplit = 1;            // "spnb-mma-split": 1 = half-precision operands carry their rounding residue (3 MMAs), 0 = plain fp16
+  int tcWarpgroups = 1;        // "spnb-tc-warpgroups": warpgroups (128 threads) per CTA of the tensor-memory layered kernel
   int interpSlots = 0;         // "spnb-interp-slots": cap on the interpreter's shared-memory value slots (0 = as many as fit)
   int groupTiles = 0;          // "spnb-group-tiles": tiles per chunk run of a chunked kernel (0 = automatic)
   int tableWindow = 0;         // "spnb-table-window": bytes of shared memory for leaf tables (0 = 64 KB)
@@ -86,7 +87,8 @@ class Engine {
   int interpSlotsCap_ = 0;
   bool layeredScalar_ = false;
   bool mmaSplit_ = true;
-  bool layeredTc5_ = false;
+  int tcWarpgroups_ = 1;
+  bool layeredTcf_ = false;
   std::string source_;
   std::vector<char> cubin_;
   std::string statsJson_;

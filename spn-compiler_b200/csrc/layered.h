@@ -37,6 +37,13 @@ struct LayeredArgs {
   const uint2* frags;
   const float* scales;
   int split;                   // 1: fragments come in (value, residue) pairs and three MMAs are issued per pair
+  int warpgroups;              // factorised tcgen05 kernel: 1, 2 or 4 warpgroups of 128 threads per CTA
+  // factorised tcgen05 kernel: the stages (eight features each) of all tensor-core leaf regions in execution
+  // order, every region padded to a multiple of four stages: input column (padding: 0) and the offset
+  // subtracted from the input.  A leaf region's MmaRegionDev::scaleOffset is its first stage in this list.
+  const int* leafCols;
+  const float* leafCentres;
+  int numLeafStages;
 };
 
 size_t layeredSmemBytes(const LayeredArgs& a, int tile);
@@ -57,12 +64,12 @@ cudaError_t layeredMmaLaunch(const LayeredArgs& a, int dtypeCode, const void* in
                              size_t smem, cudaStream_t stream);
 cudaError_t layeredMmaOccupancy(size_t smem, int* blocksPerSM);
 
-// tcgen05 / TMEM version: CTAs of 128 samples; LayeredArgs::frags holds, per full-width region, 64 k-step
-// blocks of 1 KB in the K-major non-swizzled core-matrix layout [k-half][n-group][n % 8][8 halves]
-// (MmaRegionDev::fragOffset counts 8-byte units).  *status is set to 1 if a bounded wait gave up.
-size_t layeredTc5SmemBytes(const LayeredArgs& a);
-cudaError_t layeredTc5Launch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid,
+// tcgen05 / TMEM version (layered_tcf.cu): leaf regions and inner regions both run as tensor-core
+// products with (value, residue) half-precision operands.  LayeredArgs::frags holds per leaf region stages of
+// four 1 KB k-step blocks (eight features) and per inner region blocks of four 4 KB k-step blocks (128 columns);
+// MmaRegionDev::numTiles is the number of stages / blocks.  *status is set to 1 if a bounded wait gave up.
+size_t layeredTcfSmemBytes(const LayeredArgs& a);
+cudaError_t layeredTcfLaunch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid,
                              size_t smem, int* status, cudaStream_t stream);
-cudaError_t layeredTc5Occupancy(size_t smem, int* blocksPerSM);
 
 }  // namespace spnb

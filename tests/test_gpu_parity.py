@@ -119,26 +119,34 @@ def test_interpreter_spills_values_to_scratch(capi, tmp_path):
 
 
 def test_layered_ratspn_kernel(capi, tmp_path):
-    """RAT-SPN-style region graphs are recognised and run by the layered kernel; checked against the oracle
-    and against the generic interpreter on the same plan inputs, with and without missing values."""
+    """RAT-SPN-style region graphs are recognised and run by the layered kernels (tcgen05 tensor-memory kernel
+    by default, mma.sync and scalar FP32 by name); checked against the oracle and against the generic
+    interpreter on the same inputs, with missing values and with inputs far outside half-precision range."""
     from spnb import synth
     shapes = [dict(num_features=64, depth=2, repetitions=3, width=4),
               dict(num_features=96, depth=3, repetitions=2, width=8),
               dict(num_features=70, depth=1, repetitions=2, width=32),
               dict(num_features=50, depth=2, repetitions=2, width=6),    # width not a multiple of four
-              dict(num_features=192, depth=2, repetitions=2, width=32)]  # full-width regions: tensor-core path
+              dict(num_features=192, depth=2, repetitions=2, width=32),  # full-width regions: tensor-core path
+              dict(num_features=64, depth=3, repetitions=3, width=32)]
     for sh in shapes:
         spn = synth.config5(seed=7, **sh)
         q = write_query(spn, True, directory=str(tmp_path))
         plans = {}
-        for mode in ("layered", "layered-scalar", "interp"):
+        for mode in ("layered", "layered-mma", "layered-scalar", "interp"):
             path, _ = capi.compile_query(q, _opts(True, spnb_kernel=mode))
             plans[mode] = (capi.Plan(path), path)
+        if sh["width"] == 32:
+            for wgs in (2, 4):
+                path, _ = capi.compile_query(q, _opts(True, spnb_kernel="layered", spnb_tc_warpgroups=wgs))
+                plans["layered/%d warpgroups" % wgs] = (capi.Plan(path), path)
         assert plans["layered"][0].stats["strategy"] == "layered"
         for n in (1, 129, 20001):
             x = synth.config5_inputs(n, 31, num_features=sh["num_features"])
             x[::7, ::5] = np.nan
             x[3 % n, :] = np.nan
+            x[::11, 3] = 400.0      # squares overflow half precision: the kernel's FP32 path takes the row over
+            x[::13, 5] = -1.0e4
             want = oracle_eval(q, x, True)
             for mode, (plan, _) in plans.items():
                 err = max_rel_err(plan.execute_host(x), want)
