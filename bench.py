@@ -39,10 +39,11 @@ CONFIGS = {
             marginal=True),
     3: dict(name="cfg3: 100 histogram features, ~8000 nodes, depth 10, 10% NaN, f32 log-space", n=4_000_000,
             log_space=True, marginal=True),
-    4: dict(name="cfg4: 256 mixed features, ~50000-node DAG, f32 log-space (interpreter)", n=4_000_000,
+    4: dict(name="cfg4: 256 mixed features, ~50000-node DAG, f32 log-space", n=4_000_000,
             log_space=True, marginal=True),
     5: dict(name="cfg5: RAT-SPN-style layered SPN, 784 Gaussian features, 16 repetitions, 32x1024 dense sums, f32 log-space",
-            n=2_000_000, log_space=True, marginal=True),
+            n=2_000_000, log_space=True, marginal=True,
+            layered=dict(num_features=784, depth=4, repetitions=16, width=32)),   # synth.config5's defaults
 }
 
 
@@ -290,6 +291,28 @@ def main():
             ops, peak_ops = (stats["ops_fp32"], fp32) if bound == "fp32" else (stats["ops_sfu"], sfu_rate)
         else:
             t_comp, bound, ops, peak_ops = stats["ops_fp64"] * n / fp64, "fp64", stats["ops_fp64"], fp64
+        launches = args.steps
+        if stats["strategy"] == "layered":
+            # Layered models are counted in their factorised formulation: per inner region (two operands of
+            # `width` values, `width` sums) width*2 exponentials + width logarithms and one
+            # [1 x width^2] x [width^2 x width] contraction (2 * width^3 flops); the leaf layer as a product of
+            # [x^2, x] (2 F entries) with a 2 F x width parameter matrix per repetition.  The contraction and
+            # the leaf layer run on the tensor cores, so the tensor term joins the maximum; its peak is the
+            # measured dense 16-bit GEMM rate (sustained).
+            m = cfg["layered"]
+            inner = m["repetitions"] * (2 ** m["depth"] - 1)
+            w = m["width"]
+            flops_tc = inner * 2 * w ** 3 + m["repetitions"] * 2 * w * w + 2 * (2 * m["num_features"]) * w * m["repetitions"]
+            sfu_ops = inner * 3 * w + m["repetitions"] * (2 * w + 1)
+            tc_peak = float(peaks.get("bf16_tflops_sustained", 1400.0)) * 1e12
+            t_tc = flops_tc * n / tc_peak
+            t_sfu = sfu_ops * n / min(ex2, lg2)
+            if t_tc >= t_sfu:
+                t_comp, bound, ops, peak_ops = t_tc, "tensor", flops_tc, tc_peak
+            else:
+                t_comp, bound, ops, peak_ops = t_sfu, "sfu", sfu_ops, min(ex2, lg2)
+            # per launch of the entry point: one transposition and one evaluation kernel per 512 Ki samples
+            launches = args.steps * 2 * ((n + 524287) // 524288)
         t_hbm = alg_bytes / (hbm_peak * 1e9)
         t_roof = max(t_comp, t_hbm)
         line = {
@@ -305,12 +328,12 @@ def main():
             "e2e": {"value": n * world / e2e_s, "unit": "samples/s", "h2d_bytes_per_step": int(host_x.nbytes),
                     "d2h_bytes_per_step": int(n * (4 if cfg["log_space"] else 8)), "ms_per_step": e2e_s * 1e3,
                     "kernel_ms_inside": e2e_kernel_ms, "host_buffers": "pinned", "matches_device_path": same},
-            "gpu_launches": args.steps,
+            "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": traffic, "peak_source": peak_src,
                          "note": "algorithmic bytes = %d B/sample x %d samples per launch; this workload is compute-bound, see roofline_compute" % (stats["bytes_per_sample"], n)},
             "roofline_compute": {"bound": bound, "ops_per_sample": ops, "achieved": ops * n / (ms_step * 1e-3),
-                                 "peak": peak_ops, "unit": "op/s", "frac": (ops * n / peak_ops) / (ms_step * 1e-3),
+                                 "peak": peak_ops, "unit": "flop/s" if bound == "tensor" else "op/s", "frac": (ops * n / peak_ops) / (ms_step * 1e-3),
                                  "measured_rates": {"fp32_fma": fp32, "fp32_fma_packed_pairs": fp32x2, "ex2": ex2, "lg2": lg2, "fp64_fma": fp64},
                                  "per_config_roofline_frac": t_roof / (ms_step * 1e-3), "t_roof_ms": t_roof * 1e3},
             "mean_ll": mean_ll,
