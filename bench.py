@@ -107,24 +107,33 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+def host_threads():
+    """Hardware threads this process may run on.  Asked from the scheduler and handed to the oracle
+    explicitly: under torchrun OMP_NUM_THREADS is 1, which would make the OpenMP default one thread."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_baseline(query_path, gen, cfg, seconds=12.0):
     """Times the CPU restatement of the reference's batch-vectorised path (oracle, libmvec build) on all
     host threads for a bounded sample of the workload."""
     from oracle import oracle
     model = oracle.load_model(query_path)
     mode = "log_f32_cpu" if cfg["log_space"] else "linear_f64"
-    threads = oracle.max_threads()
+    threads = host_threads()
     n = 65536
     x = gen(n, 2999)
-    oracle.evaluate(model, x[:4096], mode, vectorized=True)
+    oracle.evaluate(model, x[:4096], mode, vectorized=True, threads=threads)
     t0 = time.perf_counter()
-    oracle.evaluate(model, x, mode, vectorized=True)
+    oracle.evaluate(model, x, mode, vectorized=True, threads=threads)
     dt = time.perf_counter() - t0
     n2 = int(min(max(n * seconds / max(dt, 1e-6), n), 4_000_000))
     if n2 > n:
         x = gen(n2, 2999)
         t0 = time.perf_counter()
-        oracle.evaluate(model, x, mode, vectorized=True)
+        oracle.evaluate(model, x, mode, vectorized=True, threads=threads)
         dt = time.perf_counter() - t0
         n = n2
     return {"value": n / dt, "unit": "samples/s", "cores": threads, "kind": "port",
@@ -143,14 +152,14 @@ def run_reference(args, rank):
         query, gen = build_workload(args.config, wd)
         model = oracle.load_model(query)
     mode = "log_f32_cpu" if cfg["log_space"] else "linear_f64"
-    threads = oracle.max_threads()
+    threads = host_threads()
     n = args.ref_samples
     x = gen(n, 2000 + args.config)
     for _ in range(args.warmup):
-        oracle.evaluate(model, x, mode, vectorized=True)
+        oracle.evaluate(model, x, mode, vectorized=True, threads=threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.evaluate(model, x, mode, vectorized=True)
+        oracle.evaluate(model, x, mode, vectorized=True, threads=threads)
     dt = time.perf_counter() - t0
     val = n * args.steps / dt
     sample = "%d samples per step of the same workload, all %d host threads" % (n, threads)
