@@ -123,6 +123,13 @@ int spnb_set_device(spnb_plan* plan, int device);
 /* Launch geometry the plan uses on `device`: CTAs, threads per CTA, dynamic shared memory bytes. */
 int spnb_launch_config(spnb_plan* plan, int device, int* grid, int* block, size_t* smem_bytes);
 
+/* Waits for the work this plan has queued on `device` (all streams) and reports whether a kernel gave up on
+ * a bounded wait for the tensor cores (the tcgen05 layered kernel polls its barriers a limited number of
+ * times and raises a flag instead of hanging).  spnb_execute_host checks the flag itself; after
+ * spnb_execute_device, which returns before the kernel has run, this is the call that tells.  Returns 0 if
+ * all results are complete.  No counterpart in the reference (its kernels have no such waits). */
+int spnb_device_status(spnb_plan* plan, int device);
+
 /* Milliseconds the kernel(s) of the last spnb_execute_host call took on the device (CUDA events). */
 float spnb_last_kernel_ms(const spnb_plan* plan);
 

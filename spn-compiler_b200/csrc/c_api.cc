@@ -143,6 +143,14 @@ int spnb_launch_config(spnb_plan* plan, int device, int* grid, int* block, size_
   return guarded(SPNB_ERR_RUNTIME, [&] { plan->engine->launchConfig(device, grid, block, smem_bytes); });
 }
 
+int spnb_device_status(spnb_plan* plan, int device) {
+  if (!plan) {
+    g_lastError = "spnb_device_status: invalid argument";
+    return SPNB_ERR_ARGUMENT;
+  }
+  return guarded(SPNB_ERR_RUNTIME, [&] { plan->engine->deviceStatus(device); });
+}
+
 float spnb_last_kernel_ms(const spnb_plan* plan) { return plan ? plan->engine->lastKernelMs() : 0.f; }
 
 void spnb_plan_free(spnb_plan* plan) { delete plan; }

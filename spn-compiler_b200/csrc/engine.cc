@@ -732,6 +732,24 @@ void Engine::launchConfig(int device, int* grid, int* block, size_t* smem) {
   if (smem) *smem = st.smem;
 }
 
+// Reads (and clears) the flag the tcgen05 layered kernel raises when one of its bounded waits expires.
+// The copy is synchronous, so it also waits for the launches queued before it.
+void Engine::checkStatusFlag(DeviceState& st) {
+  if (!st.dStatus) return;
+  int flag = 0;
+  CUDA_OK(cudaMemcpy(&flag, st.dStatus, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag) {
+    cudaMemset(st.dStatus, 0, sizeof(int));
+    fail("tcgen05 layered kernel: a bounded wait on a tensor-core barrier gave up; results are incomplete");
+  }
+}
+
+void Engine::deviceStatus(int device) {
+  DeviceState& st = state(device);
+  CUDA_OK(cudaDeviceSynchronize());
+  checkStatusFlag(st);
+}
+
 // The scratch area used by launches on `stream` (allocated on first use; null if the plan needs none).
 void* Engine::scratchFor(DeviceState& st, cudaStream_t stream) {
   if (!st.scratchBytes) return nullptr;
@@ -942,14 +960,7 @@ void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, fl
     CUDA_OK(cudaEventRecord(done[c], s));
   }
   drain(nChunks);
-  if (st.dStatus) {
-    int flag = 0;
-    CUDA_OK(cudaMemcpy(&flag, st.dStatus, sizeof(int), cudaMemcpyDeviceToHost));
-    if (flag) {
-      cudaMemset(st.dStatus, 0, sizeof(int));
-      fail("tcgen05 layered kernel: a bounded wait on a tensor-core barrier gave up; results are incomplete");
-    }
-  }
+  checkStatusFlag(st);
   float total = 0.f;
   for (size_t c = 0; c < nChunks; ++c) {
     float ms = 0.f;

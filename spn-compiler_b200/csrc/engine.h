@@ -68,6 +68,7 @@ class Engine {
   void executeSharded(const int* devices, int nDevices, size_t n, const void* in, void* out, double* meanOut);
   void setDevice(int device) { hostDevice_ = device; }
   void launchConfig(int device, int* grid, int* block, size_t* smem);
+  void deviceStatus(int device);   // synchronises the device; throws if a kernel's bounded wait gave up
   float lastKernelMs() const { return lastKernelMs_; }
 
  private:
@@ -76,6 +77,7 @@ class Engine {
   DeviceState& state(int device);
   void launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cudaStream_t stream);
   void* scratchFor(DeviceState& st, cudaStream_t stream);
+  void checkStatusFlag(DeviceState& st);
   void runHostOnDevice(int device, size_t n, const void* in, void* out, float* kernelMs);
 
   Model model_;

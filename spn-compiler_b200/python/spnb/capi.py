@@ -40,6 +40,7 @@ def _load():
         "spnb_set_device": (ctypes.c_int, [vp, ctypes.c_int]),
         "spnb_launch_config": (ctypes.c_int, [vp, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
                                               ctypes.POINTER(sz)]),
+        "spnb_device_status": (ctypes.c_int, [vp, ctypes.c_int]),
         "spnb_last_kernel_ms": (ctypes.c_float, [vp]),
         "spnb_plan_free": (None, [vp]),
         "spnb_measure_peak": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
@@ -56,7 +57,7 @@ def _load():
 lib = _load()
 EXPORTS = ["spnb_compile", "spnb_plan_load", "spnb_plan_info", "spnb_plan_stats_json", "spnb_plan_source",
            "spnb_execute_host", "spnb_execute_device", "spnb_execute_device_noalloc", "spnb_execute_sharded", "spnb_set_device",
-           "spnb_launch_config", "spnb_last_kernel_ms", "spnb_plan_free", "spnb_measure_peak", "spnb_device_count", "spnb_last_error",
+           "spnb_launch_config", "spnb_device_status", "spnb_last_kernel_ms", "spnb_plan_free", "spnb_measure_peak", "spnb_device_count", "spnb_last_error",
            "spnb_version"]
 
 
@@ -147,6 +148,10 @@ class Plan:
         g, b, s = ctypes.c_int(), ctypes.c_int(), ctypes.c_size_t()
         _check(lib.spnb_launch_config(self._h, device, ctypes.byref(g), ctypes.byref(b), ctypes.byref(s)))
         return g.value, b.value, s.value
+
+    def device_status(self, device=0):
+        """Waits for the plan's queued work on `device`; raises SpnbError if a kernel gave up on a bounded wait."""
+        _check(lib.spnb_device_status(self._h, device))
 
     @property
     def last_kernel_ms(self):

@@ -189,6 +189,24 @@ def test_device_pointer_entry_matches_host_entry(capi, tmp_path):
     dout = torch.empty(x.shape[0], dtype=torch.float32, device="cuda")
     plan.execute_device(0, x.shape[0], dx.data_ptr(), dout.data_ptr(), torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    plan.device_status(0)   # no kernel of the plan gave up on a bounded wait
+    assert np.array_equal(dout.cpu().numpy(), host)
+    assert max_rel_err(host, oracle_eval(q, x, True)) <= REL_TOL_F32
+    plan.close()
+    # the same through the layered tcgen05 kernel, whose bounded-wait flag only device_status reports here
+    from spnb import synth
+    spn = synth.config5(seed=9, num_features=96, depth=3, repetitions=2, width=32)
+    q = write_query(spn, True, directory=str(tmp_path))
+    plan_path, _ = capi.compile_query(q, _opts(True))
+    plan = capi.Plan(plan_path)
+    assert plan.stats["strategy"] == "layered"
+    x = synth.config5_inputs(30001, 5, num_features=96)
+    x[::9, 1] = np.nan
+    host = plan.execute_host(x)
+    dx = torch.from_numpy(x).cuda()
+    dout = torch.empty(x.shape[0], dtype=torch.float32, device="cuda")
+    plan.execute_device(0, x.shape[0], dx.data_ptr(), dout.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    plan.device_status(0)
     assert np.array_equal(dout.cpu().numpy(), host)
     assert max_rel_err(host, oracle_eval(q, x, True)) <= REL_TOL_F32
     plan.close()
