@@ -54,6 +54,14 @@ std::string max3Tree(const std::vector<std::string>& t, size_t lo, size_t hi) {
 
 }  // namespace
 
+// Bytes of the code -> bucket byte tables the generated kernel reads: none if every table-driven group's
+// buckets are computed arithmetically.
+static size_t lutBytesNeeded(const Plan& p, const EmitOptions& opt) {
+  for (const IndexGroup& g : p.groups)
+    if (g.mode == kLut && !(g.arith && opt.bucketArith)) return p.lut.size();
+  return 0;
+}
+
 std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const Dag& d = p.dag;
   const size_t n = d.size();
@@ -78,7 +86,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     const bool nanFlags = p.marginal && p.ftype.isFloat() && p.numValueSlots > 0 && p.stats.gauss > 0;
     const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * cb + (nanFlags ? 4 : 0);
     size_t fixed = (size_t)d.numFeatures * 16 + 64;
-    if (p.lut.size() <= (size_t)opt.smemTableLimit) fixed += p.lut.size();
+    if (lutBytesNeeded(p, opt) <= (size_t)opt.smemTableLimit) fixed += lutBytesNeeded(p, opt);
     const size_t budget = 226 * 1024;  // one CTA may use up to 227 KB
     bool found = false;
     for (TILE = 1024; TILE >= 64 && !found; TILE /= 2)
@@ -107,7 +115,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const int NV = p.numValueSlots, NC = p.numCodeSlots;
   bool identity = (NC == 0 && NV == F);
   for (int f = 0; identity && f < F; ++f) identity = p.features[f].valueSlot == f;
-  const bool lutSmem = !p.lut.empty() && p.lut.size() <= (size_t)opt.smemTableLimit;
+  const size_t lutBytes = lutBytesNeeded(p, opt);
+  const bool lutSmem = lutBytes > 0 && lutBytes <= (size_t)opt.smemTableLimit;
   // Gaussian leaves of a query with marginal support must turn a NaN input into log 1 = 0: a compare
   // and a select per leaf.  NaNs are rare in practice, so the body is emitted twice: a plain version
   // and a NaN-aware one; a CTA takes the second only if one of its samples has a NaN among the staged
@@ -205,6 +214,14 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     const std::string c = "c" + std::to_string(v);
     if (G.mode == kDirect) {
       out << readCode(c, fm.codeSlot, (long long)v) << readTab(name, p.tabOffset[v], c, (long long)v);
+    } else if (G.mode == kLut && G.arith && opt.bucketArith) {
+      // bucket computed from the code; codes 0 (missing input) and 1 (outside the domain) select the two
+      // entries behind the buckets
+      const std::string b = "b" + std::to_string(v);
+      out << readCode(c, fm.codeSlot, (long long)v);
+      out << "  const int " << b << " = " << c << " < 2 ? " << (G.count + 1) << " - " << c << " : (" << c << " * " << G.arMul
+          << " + " << G.arAdd << ") >> 16;\n";
+      out << readTab(name, p.tabOffset[v], b, (long long)v);
     } else if (G.mode == kLut) {
       const std::string b = "b" + std::to_string(v);
       out << readCode(c, fm.codeSlot, (long long)v) << readLut(b, G.lutOffset, c, (long long)v)

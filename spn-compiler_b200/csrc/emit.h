@@ -17,6 +17,8 @@ struct EmitOptions {
   int chunkNodes = 2000;   // DAG nodes per generated function (0: one function)
   int groupTiles = 0;      // chunked kernels: tiles a chunk runs on back to back (0 or 1: each tile runs all chunks)
   bool useMax3 = true;     // three-input max.f32 (needs a JIT that knows PTX ISA 8.8)
+  bool bucketArith = false;  // histogram buckets by multiply-shift where that reproduces the byte table exactly
+                             // (off: five ALU instructions per leaf cost more than the shared-memory read they save)
   int smemTableLimit = 64 * 1024;  // shared-memory window for leaf tables; larger tables are streamed through it
 };
 

@@ -179,6 +179,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-group-tiles") o.groupTiles = std::atoi(v.c_str());
     else if (k == "spnb-interp-slots") o.interpSlots = std::atoi(v.c_str());
     else if (k == "spnb-mma-split") o.mmaSplit = std::atoi(v.c_str());
+    else if (k == "spnb-bucket-arith") o.bucketArith = std::atoi(v.c_str());
     else if (k == "spnb-tc-warpgroups") {
       o.tcWarpgroups = std::atoi(v.c_str());
       if (o.tcWarpgroups != 1 && o.tcWarpgroups != 2 && o.tcWarpgroups != 4) fail("spnb-tc-warpgroups must be 1, 2 or 4");
@@ -233,6 +234,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     eo.groupTiles = opt.groupTiles;
     if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
     eo.useMax3 = jitVersion() >= 1209;
+    eo.bucketArith = opt.bucketArith != 0;
     source = emitCuda(plan, eo, &ei);
     if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
     jr = jitCompile(source, m.name, opt.optLevel, opt.maxRegisters);

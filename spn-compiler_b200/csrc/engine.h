@@ -40,6 +40,7 @@ struct Options {
   int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
   int mmaSplit = 1;            // "spnb-mma-split": 1 = half-precision operands carry their rounding residue (3 MMAs), 0 = plain fp16
   int tcWarpgroups = 1;        // "spnb-tc-warpgroups": warpgroups (128 threads) per CTA of the tensor-memory layered kernel
+  int bucketArith = 0;         // "spnb-bucket-arith": 1 = compute histogram buckets by multiply-shift where exact (measured slower: off)
   int interpSlots = 0;         // "spnb-interp-slots": cap on the interpreter's shared-memory value slots (0 = as many as fit)
   int groupTiles = 0;          // "spnb-group-tiles": tiles per chunk run of a chunked kernel (0 = automatic)
   int tableWindow = 0;         // "spnb-table-window": bytes of shared memory for leaf tables (0 = 64 KB)

@@ -266,6 +266,32 @@ Plan buildPlan(const Model& m, bool logSpace) {
         while (b < g.count && x >= g.breaks[b + 1]) ++b;
         lut[2 + i] = (uint8_t)((x >= g.breaks.front() && b < g.count) ? b : g.count);
       }
+      // Is the table an affine map followed by a shift?  For every multiplier near 65536 * buckets / span the
+      // codes' constraints  lut[c] * 65536 <= c * mul + add < (lut[c] + 1) * 65536  leave an interval for add.
+      {
+        bool covered = true;   // every code of the domain falls into a bucket
+        for (int64_t c = 2; c < entries; ++c) covered = covered && lut[(size_t)c] < g.count;
+        const int64_t span = (int64_t)g.breaks.back() - g.breaks.front();
+        if (covered && span > 0) {
+          const int64_t m0 = (int64_t)std::llround(65536.0 * g.count / (double)span);
+          for (int64_t dm = 0; dm <= 256 && !g.arith; ++dm)
+            for (int sgn = 0; sgn < (dm ? 2 : 1) && !g.arith; ++sgn) {
+              const int64_t mul = m0 + (sgn ? -dm : dm);
+              if (mul <= 0) continue;
+              int64_t lo = INT64_MIN, hi = INT64_MAX;   // add in [lo, hi]
+              for (int64_t c = 2; c < entries; ++c) {
+                lo = std::max(lo, (int64_t)lut[(size_t)c] * 65536 - c * mul);
+                hi = std::min(hi, ((int64_t)lut[(size_t)c] + 1) * 65536 - 1 - c * mul);
+              }
+              if (lo > hi) continue;
+              const int64_t add = lo + (hi - lo) / 2;
+              if (entries * mul + std::llabs(add) >= (int64_t)1 << 31 || 2 * mul + add < 0) continue;
+              g.arith = true;
+              g.arMul = (int32_t)mul;
+              g.arAdd = (int32_t)add;
+            }
+        }
+      }
       auto li = lutOf.emplace(lut, (int32_t)p.lut.size());
       if (li.second) p.lut.insert(p.lut.end(), lut.begin(), lut.end());
       g.lutOffset = li.first->second;

@@ -56,6 +56,10 @@ struct IndexGroup {
   int32_t mode = kDirect;
   int32_t lutOffset = -1;        // kLut: first entry in Plan::lut (identical tables are shared)
   int32_t brkOffset = -1;        // kGeneric: first break in Plan::groupBreaks
+  // kLut groups whose byte table is reproduced exactly by  bucket = (code * arMul + arAdd) >> 16  for every
+  // code >= 2 (near-equal-width buckets): generated kernels may compute the bucket instead of loading it
+  bool arith = false;
+  int32_t arMul = 0, arAdd = 0;
 };
 
 struct PlanStats {

@@ -150,3 +150,28 @@ def test_pybind_module_and_cuda_compiler_front(tmp_path):
     with pytest.raises(RuntimeError, match="COMPILATION ERROR"):
         CUDACompiler(bogus="1").compile_ll(_toy_spn(), inputDataType="float32")
     os.remove(kernel.fileName())
+
+
+def test_histogram_buckets_can_be_computed_where_that_is_exact(tmp_path):
+    """With spnb-bucket-arith=1 near-equal-width histograms get their bucket from a multiply-shift of the
+    staged code; the byte table stays for irregular breaks and by default.  (Compilation needs no GPU.)"""
+    from spnb import capi
+    name, spn, inputs, log_space, marginal = small_configs()[3]
+    q = write_query(spn, marginal, directory=str(tmp_path))
+    on, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "unrolled",
+                                   "spnb-bucket-arith": "1"})
+    off, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "unrolled"})
+    src_on, src_off = capi.Plan(on).source, capi.Plan(off).source
+    assert src_on.count(") >> 16;") > 100 and src_off.count(") >> 16;") == 0
+    assert src_off.count("lut_s") > src_on.count("lut_s")
+    # a histogram with irregular breaks keeps its byte table
+    from spnb import synth
+    b = synth.FlatSPN(2, "float32", "two_histograms")
+    h0 = b.histogram(0, [0, 3, 50, 51, 200], [0.1, 0.2, 0.3, 0.4])
+    h1 = b.histogram(1, [0, 64, 128, 192, 256], [0.25, 0.25, 0.25, 0.25])
+    b.root = b.product([h0, h1])
+    q2 = write_query(b, True, directory=str(tmp_path))
+    p2, _ = capi.compile_query(q2, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "unrolled",
+                                    "spnb-bucket-arith": "1"})
+    src2 = capi.Plan(p2).source
+    assert src2.count(") >> 16;") == 1 and "lut_s" in src2
