@@ -247,7 +247,17 @@ def main():
     e1.record(stream)
     torch.cuda.synchronize()
     ms_total = e0.elapsed_time(e1)
+    # A short timed region ends before nvidia-smi (started with it, one line per 100 ms, 8 GPUs queried at
+    # once under torchrun) has printed a line.  The same steps then keep running, untimed, until a few samples
+    # of the clocks under this load exist; the JSON says which window the samples cover.
+    window = "timed region"
+    t_wait = time.perf_counter()
+    while len(sampler.lines) < 3 and sampler.proc is not None and time.perf_counter() - t_wait < 3.0:
+        step()
+        torch.cuda.synchronize()
+        window = "timed region and an untimed continuation of the same steps"
     clocks = sampler.stop()
+    clocks["window"] = window
     if world > 1:
         dist.barrier()
         ms_total = max_over_ranks(ms_total)
