@@ -50,3 +50,27 @@ def test_full_batch_properties(cfg, n, tmp_path):
     sub[:] = np.nan
     assert np.abs(_device_run(plan, sub)).max() <= 1e-4
     plan.close()
+
+
+def test_layered_batch_larger_than_one_transposition_chunk(tmp_path):
+    """The layered path copies the batch feature-major 512 Ki samples at a time: a batch that needs three such
+    chunks (the last one ragged) gives the same values as its pieces and as the host path, and a subset agrees
+    with the oracle."""
+    from spnb import capi, synth
+    spn = synth.config5(seed=11, num_features=64, depth=3, repetitions=2, width=32)
+    q = write_query(spn, True, directory=str(tmp_path))
+    plan_path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true"})
+    plan = capi.Plan(plan_path)
+    assert plan.stats["strategy"] == "layered"
+    n = 2 * 524288 + 70001
+    x = synth.config5_inputs(n, 17, num_features=64)
+    x[::1013, 7] = np.nan
+    whole = _device_run(plan, x)
+    plan.device_status(0)
+    assert whole.shape == (n,) and np.isfinite(whole).all()
+    idx = np.random.default_rng(6).choice(n, 5000, replace=False)
+    assert max_rel_err(whole[idx], oracle_eval(q, x[idx], True)) <= REL_TOL_F32
+    cut = 524288 + 333
+    assert np.array_equal(np.concatenate([_device_run(plan, x, 0, cut), _device_run(plan, x, cut, n)]), whole)
+    assert np.array_equal(plan.execute_host(x), whole)
+    plan.close()
