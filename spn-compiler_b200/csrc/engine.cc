@@ -168,7 +168,11 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-kernel") {
       if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar" && v != "layered-mma") fail("Unknown value '" + v + "' for option spnb-kernel");
       o.kernelMode = v;
-    } else if (k == "spnb-tile") o.tile = std::atoi(v.c_str());
+    } else if (k == "spnb-tile") {
+      o.tile = std::atoi(v.c_str());
+      if (o.tile != 0 && (o.tile < 32 || o.tile > 1024 || o.tile % 32 != 0))
+        fail("spnb-tile must be 0 (automatic) or a multiple of 32 between 32 and 1024");
+    }
     else if (k == "spnb-min-blocks") o.minBlocks = std::atoi(v.c_str());
     else if (k == "spnb-sync-every") o.syncEvery = std::atoi(v.c_str());
     else if (k == "spnb-unroll-limit") o.unrollLimit = std::atoi(v.c_str());

@@ -48,6 +48,8 @@ def test_option_handling(tmp_path):
         capi.compile_query(q, {"target": "CUDA", "no-such-option": "1"})
     with pytest.raises(capi.SpnbError, match="target"):
         capi.compile_query(q, {"use-log-space": "true"})
+    with pytest.raises(capi.SpnbError, match="spnb-tile"):
+        capi.compile_query(q, {"target": "CUDA", "spnb-tile": "100"})
     with pytest.raises(capi.SpnbError, match="CPU"):
         capi.compile_query(q, {"target": "CPU"})
     # every key the reference's Python layer may pass is accepted
