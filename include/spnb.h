@@ -98,12 +98,16 @@ int spnb_execute_device(spnb_plan* plan, int device, size_t n, const void* d_in,
  * so every GPU that loads the library gives up 32 MiB until the process exits.
  *   - Limit: the plan's image (op stream + leaf tables) plus one CTA's scratch must fit into the 32 MiB;
  *     otherwise the call fails with SPNB_ERR_RUNTIME and a message naming the limit.  n is not limited.
- *   - The first call on a device looks up the array's device address and the first call with a given plan
- *     copies that plan's image into the array (cudaMemcpyAsync on cuda_stream); make these first calls
- *     before any stream capture.
+ *   - The first call on a device looks up the array's device address.  A call copies its plan's image into
+ *     the array (cudaMemcpyAsync on cuda_stream) whenever another plan's image was the last one stored
+ *     there, i.e. on the first call with a plan and again after every switch between plans.  Make such calls
+ *     before any stream capture: while cuda_stream is capturing, a call that would have to replace the image
+ *     fails with SPNB_ERR_RUNTIME instead.
  *   - The array is shared by all plans and calls of the process and keeps the previous call's contents;
  *     nothing in it has to be cleared.  Calls that overlap on the GPU (two streams, two threads) race on it:
- *     order them.
+ *     order them.  With two different plans the race is more than a wrong result: a kernel running one
+ *     plan's program counts over the other plan's image can access memory outside its scratch.  For the
+ *     same reason a launch recorded earlier stays valid only while its plan's image is still resident.
  */
 int spnb_execute_device_noalloc(spnb_plan* plan, int device, size_t n, const void* d_in, void* d_out,
                                 void* cuda_stream);

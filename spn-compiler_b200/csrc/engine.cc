@@ -72,6 +72,39 @@ struct Driver {
   }
 };
 
+// Makes `device` current for the lifetime of the object and puts the caller's device back afterwards, also
+// when an exception unwinds through it.
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != device) {
+      CUDA_OK(cudaSetDevice(device));
+      changed = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (changed && prev >= 0) cudaSetDevice(prev);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
+// CUDA events of one host-path call; destroyed on every way out of it.
+struct EventSet {
+  std::vector<cudaEvent_t> ev;
+  cudaEvent_t add(unsigned flags) {
+    cudaEvent_t e = nullptr;
+    CUDA_OK(cudaEventCreateWithFlags(&e, flags));
+    ev.push_back(e);
+    return e;
+  }
+  ~EventSet() {
+    for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  }
+};
+
 bool parseBool(const std::string& v) {
   std::string l = v;
   std::transform(l.begin(), l.end(), l.begin(), ::tolower);
@@ -147,7 +180,7 @@ void parallelCopy(void* dst, const void* src, size_t bytes) {
 Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv) {
   static const std::set<std::string> ignored = {
       "gpu-shared-mem", "search-paths", "cpu-vectorize", "vector-library", "use-shuffle", "irOptLevel", "mcOptLevel",
-      "maxTaskSize", "slp-max-attempts", "slp-max-successful-iterations", "slp-max-node-size", "slp-max-look-ahead",
+      "slp-max-attempts", "slp-max-successful-iterations", "slp-max-node-size", "slp-max-look-ahead",
       "slp-reorder-dfs", "slp-allow-duplicate-elements", "slp-allow-topological-mixing", "slp-use-xor-chains",
       "delete-temps", "opt-repr", "stopAfter"};
   Options o;
@@ -165,6 +198,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "collect-graph-stats") o.collectStats = parseBool(v);
     else if (k == "graph-stats-file") o.statsFile = v;
     else if (k == "optLevel") o.optLevel = std::atoi(v.c_str());
+    else if (k == "maxTaskSize") o.maxTaskSize = std::atoi(v.c_str());
     else if (k == "spnb-kernel") {
       if (v != "auto" && v != "unrolled" && v != "interp" && v != "layered" && v != "layered-scalar" && v != "layered-mma") fail("Unknown value '" + v + "' for option spnb-kernel");
       o.kernelMode = v;
@@ -234,6 +268,11 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     if (opt.minBlocks) eo.minBlocksPerSM = opt.minBlocks;
     eo.syncEvery = opt.syncEvery;
     eo.gaussForm = opt.gaussForm;
+    // The reference's task partitioner (mlir/lib/Dialect/LoSPN/Passes/LoSPNTaskPartitioner.cpp:36-148) cuts the
+    // graph into tasks of at most maxTaskSize operations that hand their results on through [k x N] buffers
+    // in global memory.  The equivalent here: functions of at most that many DAG nodes over consecutive
+    // stretches of the evaluation order, results crossing a cut through the per-CTA scratch area.
+    if (opt.maxTaskSize > 0) eo.chunkNodes = opt.maxTaskSize;
     if (opt.chunkNodes >= 0) eo.chunkNodes = opt.chunkNodes;
     eo.groupTiles = opt.groupTiles;
     if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
@@ -252,8 +291,11 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     if (!source.empty()) std::fprintf(stderr, "// *** generated CUDA source ***\n%s\n// *** NVRTC log ***\n%s\n", source.c_str(), jr.log.c_str());
   }
   if (opt.collectStats) {
+    // the reference's key set first (what its tooling reads), the engine's own statistics under "spnb"
     std::ofstream f(opt.statsFile);
-    f << stats << "\n";
+    std::string ref = plan.stats.toReferenceJson();
+    ref.pop_back();
+    f << ref << ",\"spnb\":" << stats << "}\n";
   }
 
   std::string planPath = planPathIn;
@@ -423,7 +465,7 @@ Engine::DeviceState& Engine::state(int device) {
   if (ce != cudaSuccess || count == 0)
     fail("No CUDA device available: the spnb engine has no CPU fallback");
   if (device < 0 || device >= count) fail("CUDA device " + std::to_string(device) + " does not exist");
-  CUDA_OK(cudaSetDevice(device));
+  DeviceGuard guard(device);
   CUDA_OK(cudaFree(nullptr));
   std::unique_ptr<DeviceState> st(new DeviceState());
   st->device = device;
@@ -468,11 +510,11 @@ Engine::DeviceState& Engine::state(int device) {
     }
     st->dSteps = upload(steps.data(), steps.size() * sizeof(LayerStepDev));
     st->dFeat = upload(lp.features.data(), lp.features.size() * 4);
-    st->dQuad = upload(lp.quad.data(), lp.quad.size() * 4);
+    st->dQuad = upload(lp.leafParams.data(), lp.leafParams.size() * 4);
     st->dWeights = upload(lp.weights.data(), lp.weights.size() * 4);
     st->la.steps = (const LayerStepDev*)st->dSteps;
     st->la.features = (const int*)st->dFeat;
-    st->la.quad = (const float4*)st->dQuad;
+    st->la.leafParams = (const float4*)st->dQuad;
     st->la.weights = (const float*)st->dWeights;
     st->la.numSteps = (int)steps.size();
     st->la.numInputFeatures = (int)p.features.size();
@@ -502,32 +544,34 @@ Engine::DeviceState& Engine::state(int device) {
         const LayerStep& s = lp.steps[i];
         if (s.width > 32) continue;
         if (s.op == kLeafRegion) {
-          // per feature: centre = mean of the components' means; parameters re-expanded around it in double
+          // per feature: centre = mean of the components' means; the density c2 (x - mu)^2 + c1 is expanded
+          // around it in double:  c2 x'^2 + 2 c2 (centre - mu) x' + c2 (centre - mu)^2 + c1,  x' = x - centre.
+          // The expanded terms cancel against each other; with (value, residue) half-precision operands each
+          // carries about 22 bits, so a region whose constant term c2 (centre - mu)^2 exceeds 2^12 in magnitude
+          // (components many standard deviations apart) would lose more than 2^-10 per leaf and stays on the
+          // centred FP32 loop instead.
           const int F = s.numFeatures, K = s.width;
           std::vector<double> ca((size_t)F * K), cb((size_t)F * K), cc((size_t)F * K);
           bool ok = true;
           for (int f = 0; f < F; ++f) {
             double mean = 0.0;
-            int cnt = 0;
-            for (int k = 0; k < K; ++k) {
-              const float* q = lp.quad.data() + (s.paramOffset + (size_t)f * K + k) * 4;
-              if (q[0] != 0.f) { mean += -0.5 * (double)q[1] / (double)q[0]; ++cnt; }
-            }
-            const float m = cnt ? (float)(mean / cnt) : 0.f;
+            for (int k = 0; k < K; ++k) mean += (double)lp.leafParams[(s.paramOffset + (size_t)f * K + k) * 4];
+            const float m = K ? (float)(mean / K) : 0.f;
             if (!std::isfinite(m)) ok = false;
             centres[(size_t)s.featOffset + f] = m;
             for (int k = 0; k < K; ++k) {
-              const float* q = lp.quad.data() + (s.paramOffset + (size_t)f * K + k) * 4;
-              const double A = q[0], B = q[1], C = q[2], M = m;
+              const float* q = lp.leafParams.data() + (s.paramOffset + (size_t)f * K + k) * 4;
+              const double mu = q[0], c2 = q[1], c1 = q[2], dm = (double)m - mu;
               const size_t at = (size_t)f * K + k;
-              ca[at] = A;
-              cb[at] = 2.0 * A * M + B;
-              cc[at] = (A * M + B) * M + C;
+              ca[at] = c2;
+              cb[at] = 2.0 * c2 * dm;
+              cc[at] = c2 * dm * dm + c1;
               for (double v : {ca[at], cb[at], cc[at]})
                 if (!(std::fabs(v) < 60000.0)) ok = false;
+              if (!(std::fabs(c2 * dm * dm) <= 4096.0)) ok = false;
             }
           }
-          if (!ok) continue;   // parameters outside half-precision range: the kernel's FP32 loop runs the region
+          if (!ok) continue;   // the kernel's centred FP32 loop runs the region
           const int nst = (F + 7) / 8;
           mma[i].fragOffset = (long long)frags.size();
           mma[i].scaleOffset = (int)(leafCols.size() / 8);
@@ -752,6 +796,7 @@ void Engine::checkStatusFlag(DeviceState& st) {
 
 void Engine::deviceStatus(int device) {
   DeviceState& st = state(device);
+  DeviceGuard guard(device);
   CUDA_OK(cudaDeviceSynchronize());
   checkStatusFlag(st);
 }
@@ -817,9 +862,7 @@ void Engine::executeDeviceNoAlloc(int device, size_t n, const void* dIn, void* d
   if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
     fail("No CUDA device available: the spnb engine has no CPU fallback");
   if (device < 0 || device >= count) fail("CUDA device " + std::to_string(device) + " does not exist");
-  int cur = -1;
-  CUDA_OK(cudaGetDevice(&cur));
-  if (cur != device) CUDA_OK(cudaSetDevice(device));
+  DeviceGuard guard(device);
   std::lock_guard<std::mutex> lock(noAllocMu_);
   int optin = 0;
   CUDA_OK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
@@ -872,17 +915,13 @@ void Engine::executeDeviceNoAlloc(int device, size_t n, const void* dIn, void* d
   img.tag = noAllocTag_;
   const char* why = nullptr;
   cudaError_t e = interpLaunchStatic(img, ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, noAllocTile_, device, stream, &why);
-  if (cur != device && cur >= 0) cudaSetDevice(cur);
   if (e != cudaSuccess) fail(why ? std::string("spnb_execute_device_noalloc: ") + why : std::string("CUDA error: ") + cudaGetErrorString(e));
 }
 
 void Engine::executeDevice(int device, size_t n, const void* dIn, void* dOut, cudaStream_t stream) {
   DeviceState& st = state(device);
-  int cur = -1;
-  CUDA_OK(cudaGetDevice(&cur));
-  if (cur != device) CUDA_OK(cudaSetDevice(device));
+  DeviceGuard guard(device);
   launch(st, n, dIn, dOut, stream);
-  if (cur != device && cur >= 0) CUDA_OK(cudaSetDevice(cur));
 }
 
 // Host-resident batch on one device: chunks are copied to pinned staging (unless the caller's
@@ -893,7 +932,7 @@ void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, fl
   if (n == 0) return;
   DeviceState& st = state(device);
   std::lock_guard<std::mutex> hostLock(st.hostMu);
-  CUDA_OK(cudaSetDevice(device));
+  DeviceGuard guard(device);
   const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature;
   const size_t resBytes = meta_.bytesPerResult;
   size_t chunkRows = std::max<size_t>((size_t)(48u << 20) / std::max<size_t>(rowBytes, 1), 4096);
@@ -930,11 +969,12 @@ void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, fl
   }
   if (!outPinned && !st.hOut) CUDA_OK(cudaHostAlloc(&st.hOut, st.outBytes, cudaHostAllocDefault));
 
+  EventSet events;
   std::vector<cudaEvent_t> k0(nChunks), k1(nChunks), done(nChunks);
   for (size_t c = 0; c < nChunks; ++c) {
-    CUDA_OK(cudaEventCreate(&k0[c]));
-    CUDA_OK(cudaEventCreate(&k1[c]));
-    CUDA_OK(cudaEventCreateWithFlags(&done[c], cudaEventDisableTiming));
+    k0[c] = events.add(cudaEventDefault);
+    k1[c] = events.add(cudaEventDefault);
+    done[c] = events.add(cudaEventDisableTiming);
   }
   char* hostOut = outPinned ? (char*)out : (char*)st.hOut;
   size_t drained = 0;  // chunks whose results have been handed to the caller
@@ -971,9 +1011,6 @@ void Engine::runHostOnDevice(int device, size_t n, const void* in, void* out, fl
   for (size_t c = 0; c < nChunks; ++c) {
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, k0[c], k1[c]) == cudaSuccess) total += ms;
-    cudaEventDestroy(k0[c]);
-    cudaEventDestroy(k1[c]);
-    cudaEventDestroy(done[c]);
   }
   if (kernelMs) *kernelMs = total;
 }

@@ -29,6 +29,7 @@ struct Options {
   bool dumpIR = false;         // "dump-ir": print the generated CUDA source and the plan statistics
   bool collectStats = false;   // "collect-graph-stats"
   std::string statsFile = "/tmp/stats.json";
+  int maxTaskSize = -1;        // "maxTaskSize": > 0 caps the DAG nodes per generated function (the reference's task size)
   int optLevel = 3;            // "optLevel"
   std::string kernelMode = "auto";  // "spnb-kernel": auto | unrolled | interp | layered | layered-mma | layered-scalar
   int tile = 0;                // "spnb-tile": threads per CTA (0 = default)

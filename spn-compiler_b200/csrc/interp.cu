@@ -189,10 +189,8 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
 template <typename in_t>
 cudaError_t launchT(const InterpArgs& a, const void* in, float* out, size_t n, int grid, int tile, size_t smem,
                     cudaStream_t stream) {
-  if (smem > 48 * 1024) {  // per device and per instantiation; cheap enough to repeat
-    cudaError_t e = cudaFuncSetAttribute(interpKernel<in_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<in_t>), smem);
+  if (e != cudaSuccess) return e;
   interpKernel<in_t><<<grid, tile, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n);
   return cudaGetLastError();
 }
@@ -206,10 +204,8 @@ size_t interpSmemBytes(const InterpArgs& a, int tile) {
 cudaError_t interpOccupancy(int inKindCode, int tile, size_t smem, int* blocksPerSM) {
   // all instantiations have the same resource usage up to the staging conversion; query the float one
   (void)inKindCode;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(interpKernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<float>), smem);
+  if (e != cudaSuccess) return e;
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, interpKernel<float>, tile, smem);
 }
 
@@ -233,9 +229,9 @@ cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, flo
 // =========================================================================================================
 // Interpreter without device allocations.
 //
-// Some callers must not allocate device memory at the time they run a model: code inside a CUDA-graph
-// capture or a latency-critical serving loop (cudaMalloc synchronises the device and is illegal during
-// capture), and hosts that hand this library a fixed memory budget up front.  For them the interpreter
+// Some callers must not allocate device memory at the time they run a model: a latency-critical serving
+// loop (cudaMalloc synchronises the whole device), and hosts that hand this library a fixed memory budget
+// up front.  For them the interpreter
 // can run with everything it needs besides the caller's input and output buffers placed in one
 // file-scope device array: first the model image (op stream, leaf tables, byte tables, breaks, feature
 // descriptors), then the per-CTA spill scratch.  The array's size is fixed (kStaticAreaBytes); a model
@@ -245,7 +241,12 @@ cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, flo
 // The array is shared by every call in the process and keeps whatever the last call left in it.  Nothing
 // in it needs to start at zero: the image is rewritten when a different plan ran last, and every scratch
 // slot is written before it is read within one tile.  Two calls that overlap on the GPU (different
-// streams, or different host threads) race on it: callers must order them.
+// streams, or different host threads) race on it: callers must order them.  The race is not benign when the
+// calls belong to different plans: a kernel launched with one plan's counts would then walk the other
+// plan's op stream, whose slot and table indices it does not re-check, and may read or write outside its
+// scratch.  Which image is resident is tracked on the host when a call is enqueued; a launch that is
+// replayed later (a captured stream) is only valid while its plan's image is still the resident one, so an
+// image swap is refused while the stream is capturing.
 // =========================================================================================================
 namespace {
 
@@ -287,6 +288,13 @@ cudaError_t interpLaunchStatic(const InterpImage& img, InterpArgs a, int dtypeCo
     return cudaErrorInvalidValue;
   }
   if (st.resident != img.tag) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      if (message) *message = "another plan's image is resident in the static device area and cannot be replaced while "
+                              "the stream is capturing: run this plan once before the capture";
+      return cudaErrorInvalidValue;
+    }
     cudaError_t e = cudaSuccess;
     auto put = [&](size_t off, const void* src, size_t bytes) {
       if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(st.base + off, src, bytes, cudaMemcpyHostToDevice, stream);

@@ -4,6 +4,10 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "plan.h"
 
 namespace spnb {
@@ -32,6 +36,23 @@ struct InterpArgs {
     return (o + 3) & ~(size_t)3;
   }
 };
+
+// Raises a kernel's dynamic shared-memory limit to `smem` bytes on the current device.  The attribute is
+// per device and per function and only ever needs to grow, so the driver is called the first time and when
+// a larger size is asked for, not on every launch.
+inline cudaError_t ensureDynamicSmem(const void* kernel, size_t smem) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, size_t> granted;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& have = granted[std::make_pair(device, kernel)];
+  if (smem <= have || smem <= 48 * 1024) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) have = smem;
+  return e;
+}
 
 size_t interpSmemBytes(const InterpArgs& a, int tile);
 cudaError_t interpOccupancy(int dtypeCode, int tile, size_t smem, int* blocksPerSM);

@@ -3,7 +3,7 @@
 //
 // One thread per sample, CTAs of `tile` samples.  The region tree is walked in post-order as a stack
 // machine whose entries are the (up to 32) outputs of one region, kept in shared memory [level][k][tile]:
-//   leaf region   out_k = sum_f a_kf x_f^2 + b_kf x_f + c_kf         (factorised Gaussians, base-2 logs)
+//   leaf region   out_k = sum_f c2_kf (x_f - mu_kf)^2 + c1_kf        (factorised Gaussians, base-2 logs)
 //   inner region  out_k = ma + mb + log2( sum_i ea_i * sum_j W_k[i,j] * eb_j ),  ea = 2^(a - ma), eb = 2^(b - mb)
 // i.e. the cross products of two child regions are never materialised: 2^(a_i + b_j - ma - mb) factorises
 // into ea_i * eb_j, which turns wa*wb exponentials per sum into wa + wb per region and leaves a small
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
       if (s.op == kLeafRegion) {
         const int cnt = s.numFeatures * s.width;
         __syncthreads();
-        for (int i = tid; i < cnt; i += T) pbuf[i] = a.quad[s.paramOffset + i];
+        for (int i = tid; i < cnt; i += T) pbuf[i] = a.leafParams[s.paramOffset + i];
         __syncthreads();
         float acc[KMAX];
 #pragma unroll
@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
     #pragma unroll
                 for (int k = 0; k < KMAX; ++k) {
                   const float4 q = p[k];
-                  const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                  const float dx = xv - q.x;
+                  const float t = fmaf(dx * dx, q.y, q.z);
                   acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
                 }
               } else {
@@ -97,7 +98,8 @@ __global__ void __launch_bounds__(256) layeredKernel(LayeredArgs a, const in_t* 
                 for (int k = 0; k < KMAX; ++k) {
                   if (k < s.width) {
                     const float4 q = p[k];
-                    const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                    const float dx = xv - q.x;
+                  const float t = fmaf(dx * dx, q.y, q.z);
                     acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
                   }
                 }
@@ -212,10 +214,8 @@ template <typename in_t>
 cudaError_t launchT(const LayeredArgs& a, const void* in, float* out, size_t n, int grid, int tile, size_t smem,
                     cudaStream_t stream) {
   auto run = [&](auto kernel) -> cudaError_t {
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return e;
-    }
+    cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(kernel), smem);
+    if (e != cudaSuccess) return e;
     kernel<<<grid, tile, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n);
     return cudaGetLastError();
   };
@@ -272,10 +272,8 @@ size_t layeredSmemBytes(const LayeredArgs& a, int tile) {
 }
 
 cudaError_t layeredOccupancy(int tile, size_t smem, int* blocksPerSM) {
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(layeredKernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&layeredKernel<float, true>), smem);
+  if (e != cudaSuccess) return e;
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, layeredKernel<float, true>, tile, smem);
 }
 

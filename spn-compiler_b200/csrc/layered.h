@@ -24,7 +24,7 @@ struct MmaRegionDev {
 struct LayeredArgs {
   const LayerStepDev* steps;
   const int* features;
-  const float4* quad;      // per (feature, k): a, b, c of  a*x^2 + b*x + c  (base-2 log density)
+  const float4* leafParams;   // per (feature, k): (mu, c2, c1, 0) of  c2*(x - mu)^2 + c1  (base-2 log density)
   const float* weights;
   int numSteps;
   int numInputFeatures;    // columns of the input matrix

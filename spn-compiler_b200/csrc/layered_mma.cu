@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(TM, 1) layeredMmaKernel(LayeredArgs a, const i
       if (s.op == kLeafRegion) {
         const int cnt = s.numFeatures * s.width;
         __syncthreads();
-        for (int i = tid; i < cnt; i += TM) pbuf[i] = a.quad[s.paramOffset + i];
+        for (int i = tid; i < cnt; i += TM) pbuf[i] = a.leafParams[s.paramOffset + i];
         __syncthreads();
         float acc[KMAX];
 #pragma unroll
@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(TM, 1) layeredMmaKernel(LayeredArgs a, const i
     #pragma unroll
                 for (int k = 0; k < KMAX; ++k) {
                   const float4 q = p[k];
-                  const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                  const float dx = xv - q.x;
+                  const float t = fmaf(dx * dx, q.y, q.z);
                   acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
                 }
               } else {
@@ -129,7 +130,8 @@ __global__ void __launch_bounds__(TM, 1) layeredMmaKernel(LayeredArgs a, const i
                 for (int k = 0; k < KMAX; ++k) {
                   if (k < s.width) {
                     const float4 q = p[k];
-                    const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                    const float dx = xv - q.x;
+                  const float t = fmaf(dx * dx, q.y, q.z);
                     acc[k] = MARGINAL ? fmaf(m, t, acc[k]) : acc[k] + t;
                   }
                 }
@@ -342,7 +344,7 @@ template <typename in_t>
 cudaError_t launchT(const LayeredArgs& a, const void* in, float* out, size_t n, int grid, size_t smem, int bufBytes,
                     cudaStream_t stream) {
   auto run = [&](auto kernel) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(kernel), smem);
     if (e != cudaSuccess) return e;
     kernel<<<grid, TM, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n, bufBytes);
     return cudaGetLastError();
@@ -365,7 +367,7 @@ size_t layeredMmaSmemBytes(const LayeredArgs& a) {
 }
 
 cudaError_t layeredMmaOccupancy(size_t smem, int* blocksPerSM) {
-  cudaError_t e = cudaFuncSetAttribute(layeredMmaKernel<float, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&layeredMmaKernel<float, true, true>), smem);
   if (e != cudaSuccess) return e;
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, layeredMmaKernel<float, true, true>, TM, smem);
 }

@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(TS * NWG + 32, 1) layeredTcfKernel(LayeredArgs
           // tensor weights)
 #pragma unroll
           for (int k = 0; k < KPW; ++k) r[k] = 0u;
-          const float4* __restrict__ pbuf = a.quad + s.paramOffset;
+          const float4* __restrict__ pbuf = a.leafParams + s.paramOffset;
           for (int f = 0; f < s.numFeatures; ++f) {
             const int col = __ldg(a.features + s.featOffset + f);
             float xv = a.xtLd ? xT[(size_t)col * a.xtLd] : (float)x[col];
@@ -399,7 +399,8 @@ __global__ void __launch_bounds__(TS * NWG + 32, 1) layeredTcfKernel(LayeredArgs
             for (int k = 0; k < KPW; ++k) {
               if (wg * KPW + k < s.width) {
                 const float4 q = __ldg(p + k);
-                const float t = fmaf(fmaf(q.x, xv, q.y), xv, q.z);
+                const float dx = xv - q.x;
+                const float t = fmaf(dx * dx, q.y, q.z);
                 const float acc = __uint_as_float(r[k]);
                 r[k] = __float_as_uint(MARGINAL ? fmaf(m, t, acc) : acc + t);
               }
@@ -636,7 +637,7 @@ template <typename in_t>
 cudaError_t launchT(const LayeredArgs& a, const void* in, float* out, size_t n, int grid, size_t smem, int* status,
                     cudaStream_t stream) {
   auto run = [&](auto kernel) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(kernel), smem);
     if (e != cudaSuccess) return e;
     kernel<<<grid, TS * a.warpgroups + 32, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n, status);
     return cudaGetLastError();

@@ -66,9 +66,9 @@ struct Recogniser {
       s.width = (int32_t)nodes.size();
       s.numFeatures = (int32_t)nf;
       s.featOffset = (int64_t)lp.features.size();
-      s.paramOffset = (int64_t)lp.quad.size() / 4;
+      s.paramOffset = (int64_t)lp.leafParams.size() / 4;
       lp.features.insert(lp.features.end(), feats.begin(), feats.end());
-      lp.quad.resize(lp.quad.size() + 4 * (size_t)nf * nodes.size(), 0.f);
+      lp.leafParams.resize(lp.leafParams.size() + 4 * (size_t)nf * nodes.size(), 0.f);
       const double LOG2E = 1.4426950408889634074;
       for (size_t k = 0; k < nodes.size(); ++k) {
         const int32_t v = nodes[k];
@@ -79,11 +79,10 @@ struct Recogniser {
           const double sd = d.stddev[g], mu = d.mean[g];
           const double c2 = -(1.0 / (2.0 * sd * sd)) * LOG2E;
           const double c1 = (-std::log(sd) - 0.5 * std::log(2 * M_PI)) * LOG2E;
-          // c1 + c2 (x - mu)^2 = c2 x^2 - 2 c2 mu x + (c1 + c2 mu^2)
           const size_t q = 4 * ((size_t)s.paramOffset + (size_t)f * nodes.size() + k);
-          lp.quad[q] = (float)c2;
-          lp.quad[q + 1] = (float)(-2.0 * c2 * mu);
-          lp.quad[q + 2] = (float)(c1 + c2 * mu * mu);
+          lp.leafParams[q] = (float)mu;
+          lp.leafParams[q + 1] = (float)c2;
+          lp.leafParams[q + 2] = (float)c1;
         }
       }
       lp.maxWidth = std::max(lp.maxWidth, s.width);

@@ -10,7 +10,7 @@
 namespace spnb {
 
 // One step of the layered program (a stack machine over region outputs, post-order over the region tree).
-//   kLeafRegion:  push `width` values:  out_k = sum_f (a_kf * x_f + b_kf) * x_f + c_kf
+//   kLeafRegion:  push `width` values:  out_k = sum_f c2_kf * (x_f - mu_kf)^2 + c1_kf
 //   kInnerRegion: pop b (top, width wb), pop a (width wa), push `width` values:
 //                 out_k = max(a) + max(b) + log2( sum_ij W_k[i*wb+j] * 2^(a_i - max a) * 2^(b_j - max b) )
 //   kRootPart:    like kInnerRegion with one output, which is folded into the running root log-sum
@@ -22,13 +22,14 @@ struct LayerStep {
   int32_t wa = 0, wb = 0;     // widths of the two operands (inner / root part)
   int32_t numFeatures = 0;    // leaf region
   int64_t featOffset = 0;     // leaf: first entry in LayeredPlan::features
-  int64_t paramOffset = 0;    // leaf: first 4-float entry in quad (layout [feature][k]); inner: first float in weights
+  int64_t paramOffset = 0;    // leaf: first 4-float entry in leafParams (layout [feature][k]); inner: first float in weights
 };
 
 struct LayeredPlan {
   std::vector<LayerStep> steps;
   std::vector<int32_t> features;   // input columns of the leaf regions
-  std::vector<float> quad;         // (a, b, c, 0) of the expanded Gaussian log2-density a*x^2 + b*x + c
+  std::vector<float> leafParams;   // (mu, c2, c1, 0) of the Gaussian log2-density c2*(x - mu)^2 + c1: the centred form the
+                                   // reference evaluates (an expanded quadratic cancels badly when |mu| >> stddev)
   std::vector<float> weights;      // linear-space sum weights, [k][i*wb + j]
   int32_t maxWidth = 0;
   int32_t maxDepth = 0;            // deepest the region stack gets

@@ -51,8 +51,28 @@ Dag canonicalize(const Model& m) {
   std::vector<int32_t> uNode;  // unique id -> a representative model node
   std::vector<int64_t> uChildPtr{0};
   std::vector<int32_t> uChild;
-  std::unordered_map<Key128, int32_t, KeyHash> seen;
+  std::unordered_multimap<Key128, int32_t, KeyHash> seen;
   seen.reserve(n * 2);
+  // structural equality of model node v with the representative of unique node u (the hash only nominates)
+  auto sameNode = [&](size_t v, int32_t u) {
+    const int32_t r = uNode[(size_t)u];
+    if (m.kind[v] != m.kind[r]) return false;
+    const int64_t lo = m.childPtr[v], hi = m.childPtr[v + 1], rlo = m.childPtr[r];
+    if (hi - lo != m.childPtr[r + 1] - rlo) return false;
+    if (m.kind[v] == kProduct || m.kind[v] == kSum) {
+      for (int64_t e = 0; e < hi - lo; ++e) {
+        if (canon[m.childIdx[lo + e]] != uChild[(size_t)(uChildPtr[(size_t)u] + e)]) return false;
+        if (m.kind[v] == kSum && m.weight[lo + e] != m.weight[rlo + e]) return false;
+      }
+      return true;
+    }
+    if (m.feature[v] != m.feature[r]) return false;
+    if (m.kind[v] == kGaussian) return m.mean[v] == m.mean[r] && m.stddev[v] == m.stddev[r];
+    const int64_t nt = m.tabPtr[v + 1] - m.tabPtr[v], nb = m.brkPtr[v + 1] - m.brkPtr[v];
+    if (nt != m.tabPtr[r + 1] - m.tabPtr[r] || nb != m.brkPtr[r + 1] - m.brkPtr[r]) return false;
+    return std::equal(m.tab.begin() + m.tabPtr[v], m.tab.begin() + m.tabPtr[v + 1], m.tab.begin() + m.tabPtr[r]) &&
+           std::equal(m.brk.begin() + m.brkPtr[v], m.brk.begin() + m.brkPtr[v + 1], m.brk.begin() + m.brkPtr[r]);
+  };
   for (size_t v = 0; v < n; ++v) {
     int64_t lo = m.childPtr[v], hi = m.childPtr[v + 1];
     uint8_t kind = m.kind[v];
@@ -62,6 +82,7 @@ Dag canonicalize(const Model& m) {
     }
     Hasher h;
     h.add(kind);
+    h.add((uint64_t)(hi - lo));
     if (kind == kProduct || kind == kSum) {
       for (int64_t e = lo; e < hi; ++e) {
         h.add((uint64_t)(uint32_t)canon[m.childIdx[e]]);
@@ -73,15 +94,21 @@ Dag canonicalize(const Model& m) {
         h.addDouble(m.mean[v]);
         h.addDouble(m.stddev[v]);
       } else {
+        h.add((uint64_t)(m.tabPtr[v + 1] - m.tabPtr[v]));
         for (int64_t t = m.tabPtr[v]; t < m.tabPtr[v + 1]; ++t) h.addDouble(m.tab[t]);
         for (int64_t t = m.brkPtr[v]; t < m.brkPtr[v + 1]; ++t) h.add((uint64_t)(uint32_t)m.brk[t]);
       }
     }
-    auto ins = seen.emplace(h.key(), (int32_t)uNode.size());
-    if (!ins.second) {
-      canon[v] = ins.first->second;
+    const Key128 key = h.key();
+    int32_t found = -1;
+    auto range = seen.equal_range(key);
+    for (auto it = range.first; it != range.second && found < 0; ++it)
+      if (sameNode(v, it->second)) found = it->second;
+    if (found >= 0) {
+      canon[v] = found;
       continue;
     }
+    seen.emplace(key, (int32_t)uNode.size());
     canon[v] = (int32_t)uNode.size();
     uNode.push_back((int32_t)v);
     for (int64_t e = lo; e < hi; ++e) uChild.push_back(canon[m.childIdx[e]]);
@@ -186,6 +213,16 @@ std::string PlanStats::toJson() const {
     << ",\"sum_edges\":" << sumEdges << ",\"product_edges\":" << productEdges << ",\"depth\":" << depth
     << ",\"ops_sfu\":" << opsSfu << ",\"ops_fp32\":" << opsFp32 << ",\"ops_fp64\":" << opsFp64
     << ",\"bytes_per_sample\":" << bytesPerSample << "}";
+  return o.str();
+}
+
+std::string PlanStats::toReferenceJson() const {
+  std::ostringstream o;
+  o << "{\"featureCount\":" << featureCount << ",\"minDepth\":" << minDepth << ",\"maxDepth\":" << maxDepth
+    << ",\"averageDepth\":" << averageDepth << ",\"medianDepth\":" << medianDepth
+    << ",\"innerCount\":" << (refAdds + refMuls) << ",\"leafCount\":" << (gauss + cats + hists + refConstants)
+    << ",\"sumCount\":" << refAdds << ",\"productCount\":" << refMuls << ",\"categoricalCount\":" << cats
+    << ",\"constantCount\":" << refConstants << ",\"gaussianCount\":" << gauss << ",\"histogramCount\":" << hists << "}";
   return o.str();
 }
 
@@ -353,6 +390,43 @@ Plan buildPlan(const Model& m, bool logSpace) {
   s.opsFp32 += s.opsSfu;
   s.opsFp64 += 40;
   s.depth = depth[n - 1];
+  {
+    // reference-style statistics on the two-input form: an operand at position i of k sits
+    // ceil(log2 k) levels (at most) below its node in the balanced tree; sum operands one more (the
+    // multiplication by the weight)
+    s.featureCount = d.numFeatures;
+    std::vector<int64_t> level(n, -1);
+    level[n - 1] = 0;
+    std::vector<double> constants;
+    for (size_t v = n; v-- > 0;) {
+      if (level[v] < 0) continue;
+      const int64_t k = d.childPtr[v + 1] - d.childPtr[v];
+      if (k == 0) continue;
+      int64_t lg = 0;
+      while (((int64_t)1 << lg) < k) ++lg;
+      const bool sum = d.kind[v] == kSum;
+      if (sum) { s.refAdds += k - 1; s.refMuls += k; } else { s.refMuls += k - 1; }
+      for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
+        level[d.childIdx[e]] = std::max(level[d.childIdx[e]], level[v] + lg + (sum ? 1 : 0));
+        if (sum) constants.push_back(d.weight[e]);
+      }
+    }
+    std::sort(constants.begin(), constants.end());
+    s.refConstants = (int64_t)(std::unique(constants.begin(), constants.end()) - constants.begin());
+    std::vector<int64_t> leafLevels;
+    for (size_t v = 0; v < n; ++v)
+      if (d.childPtr[v + 1] == d.childPtr[v] && level[v] >= 0) leafLevels.push_back(level[v]);
+    if (!leafLevels.empty()) {
+      std::sort(leafLevels.begin(), leafLevels.end());
+      s.minDepth = leafLevels.front();
+      s.maxDepth = leafLevels.back();
+      double acc = 0.0;
+      for (int64_t l : leafLevels) acc += (double)l;
+      s.averageDepth = acc / (double)leafLevels.size();
+      const size_t h = leafLevels.size() / 2;
+      s.medianDepth = leafLevels.size() % 2 ? (double)leafLevels[h] : 0.5 * (double)(leafLevels[h - 1] + leafLevels[h]);
+    }
+  }
   s.bytesPerSample = (int64_t)m.numFeatures * m.ftype.bytes() + (logSpace ? 4 : 8);
 
   if (logSpace) buildProgram(p, INT32_MAX);

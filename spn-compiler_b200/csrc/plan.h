@@ -72,7 +72,18 @@ struct PlanStats {
   int64_t opsFp32 = 0;        // 3/gauss + 2/discrete leaf + (k-1)/product + (4k-1)/sum + opsSfu
   int64_t opsFp64 = 0;        // linear f64 formulation: (k-1)/product + (2k-1)/sum + leaves + 40 (root log)
   int64_t bytesPerSample = 0; // F * sizeof(input) + sizeof(output)
+  // The reference's graph statistics (mlir/lib/Dialect/LoSPN/Passes/LoSPNGraphStatsCollection.cpp:83-102),
+  // counted on the form the reference lowers to: a product / weighted sum with k operands is a balanced tree
+  // of k-1 two-input multiplications / additions, every sum operand is first multiplied by a weight constant
+  // (equal constants are one node after CSE).  Depths are the levels of the distinct leaves below the root
+  // (root = level 0) in that two-input form.
+  int64_t featureCount = 0, refAdds = 0, refMuls = 0, refConstants = 0;
+  int64_t minDepth = 0, maxDepth = 0;
+  double averageDepth = 0.0, medianDepth = 0.0;
   std::string toJson() const;
+  // JSON object with exactly the reference's keys: featureCount, minDepth, maxDepth, averageDepth, medianDepth,
+  // innerCount, leafCount, sumCount, productCount, categoricalCount, constantCount, gaussianCount, histogramCount
+  std::string toReferenceJson() const;
 };
 
 // Interpreter program: a flat int32 stream, all operands are value slots.

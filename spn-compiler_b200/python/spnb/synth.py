@@ -258,12 +258,13 @@ class ArraySPN:
                                    "support_marginal": support_marginal})
 
 
-def config5(seed=1005, num_features=784, depth=4, repetitions=16, width=32):
+def config5(seed=1005, num_features=784, depth=4, repetitions=16, width=32, mean_dist=(0.5, 0.3), sd_range=(0.2, 1.0)):
     """RAT-SPN-style layered SPN: `repetitions` random balanced region trees of depth `depth` over
     `num_features` features; every leaf region carries `width` factorised Gaussian distributions, every
     inner region `width` sum nodes over the width x width cross products of its two child regions (dense
     width x width^2 weights ~ Dirichlet(1)); one root sum mixes the root products of all repetitions.
-    The full size (784, 4, 16, 32) has ~660 k nodes and ~7.4 M sum edges."""
+    The full size (784, 4, 16, 32) has ~660 k nodes and ~7.4 M sum edges.  Leaf means ~ N(mean_dist[0], mean_dist[1]),
+    standard deviations ~ U(sd_range[0], sd_range[1])."""
     rng = np.random.default_rng(seed)
     K, F = width, num_features
     kind, scope_id, mean, stddev, cnt, child, weight = [], [], [], [], [], [], []
@@ -291,7 +292,7 @@ def config5(seed=1005, num_features=784, depth=4, repetitions=16, width=32):
         for feats in regions:
             nf = len(feats)
             g = add(wire.K_GAUSS, K * nf, np.zeros(K * nf), None, scope=np.tile(feats, K),
-                    mu=rng.normal(0.5, 0.3, K * nf), sd=rng.uniform(0.2, 1.0, K * nf))
+                    mu=rng.normal(mean_dist[0], mean_dist[1], K * nf), sd=rng.uniform(sd_range[0], sd_range[1], K * nf))
             level.append(add(wire.K_PRODUCT, K, np.full(K, nf), g.reshape(K, nf)))
         for d in range(depth - 1, -1, -1):
             nxt = []

@@ -1,14 +1,15 @@
 """Binary (Cap'n Proto) serialisation of SPN models and queries.
 
-Same surface as the reference's xspn/xspn/serialization/binary/BinarySerialization.py:53-81
-(`BinarySerializer(fileName).serialize_to_file(modelOrQuery)`), and the same steps before
-writing (:106-129): validity check, file-unique ids, bottom-up scope rebuild, nodes listed
-children-before-parents.  The encoding itself is done by `wire.encode_flat` (no pycapnp).
+Same surface as the reference's xspn/xspn/serialization/binary/BinarySerialization.py:53-81 and :254-370
+(`BinarySerializer(fileName).serialize_to_file(modelOrQuery)`,
+`BinaryDeserializer(fileName).deserialize_from_file()`), and the same steps before writing (:106-129):
+validity check, file-unique ids, bottom-up scope rebuild, nodes listed children-before-parents.
+The encoding and decoding themselves are done by `wire` (no pycapnp).
 """
 import numpy as np
 
 from xspn.structure.Model import SPNModel
-from xspn.structure.Query import ErrorKind, JointProbability, Query
+from xspn.structure.Query import ErrorKind, ErrorModel, JointProbability, Query
 from xspn.structure import Nodes
 from xspn.serialization.binary import wire
 
@@ -115,3 +116,65 @@ class BinarySerializer:
             root_id=root.id, scope=[int(_item(s)) for s in root.scope], feature_type=str(model.featureType),
             name=model.name or "", query=query, repr_ptr=repr_ptr, repr_pts=np.asarray(repr_pts, np.float64),
             hist_type=hist_type, hist_meta=hist_meta)
+
+
+_TYPE_NAME = {v: k for k, v in _TYPE_ORD.items()}
+_META_NAME = {v: k for k, v in _META_ORD.items()}
+
+
+class BinaryDeserializer:
+    """Read an SPNModel or a JointProbability query back from an xspn binary file.
+
+    Nodes come back as xspn.structure.Nodes objects (SPFlow's attribute names), children resolved by id,
+    scopes rebuilt bottom-up and the structure checked, as the reference does after reading
+    (BinarySerialization.py:295-312).  Histogram `type` / `meta_type` come back as the lower-case names of
+    the schema's enumerants."""
+
+    def __init__(self, fileName):
+        self.fileName = fileName
+
+    def deserialize_from_file(self):
+        with open(self.fileName, "rb") as f:
+            return self.deserialize_from_bytes(f.read())
+
+    def deserialize_from_bytes(self, data):
+        msg = wire.decode_message(data)
+        model = self._model(msg)
+        q = msg["query"]
+        if q is None:
+            return model
+        if q["error_kind"] == 0:
+            kind = ErrorKind.ABSOLUTE
+        elif q["error_kind"] == 1:
+            kind = ErrorKind.RELATIVE
+        else:
+            raise NotImplementedError("Cannot deserialize error kind %r" % (q["error_kind"],))
+        return JointProbability(model, q["batch_size"], q["support_marginal"], ErrorModel(kind, q["max_error"]))
+
+    def _model(self, msg):
+        by_id, roots = {}, []
+        for nd in msg["nodes"]:
+            k = nd["kind"]
+            if k in (wire.K_PRODUCT, wire.K_SUM):
+                kids = [by_id.get(c) for c in nd["children"]]
+                assert None not in kids, "Child node ID could not be resolved"
+                node = Nodes.Product(children=kids) if k == wire.K_PRODUCT else Nodes.Sum(weights=nd["weights"], children=kids)
+            elif k == wire.K_HIST:
+                node = Nodes.Histogram(nd["breaks"], nd["densities"], nd["bin_repr_points"], scope=nd["scope"],
+                                       type_=_TYPE_NAME.get(nd["type"]), meta_type=_META_NAME.get(nd["meta_type"]))
+            elif k == wire.K_GAUSS:
+                node = Nodes.Gaussian(nd["mean"], nd["stddev"], nd["scope"])
+            else:
+                node = Nodes.Categorical(p=nd["probabilities"], scope=nd["scope"])
+            node.id = nd["id"]
+            by_id[node.id] = node
+            if nd["root"]:
+                roots.append(node)
+        for r in roots:
+            Nodes.rebuild_scopes_bottom_up(r)
+            ok, why = Nodes.is_valid(r)
+            assert ok, "SPN invalid after deserialization: %s" % why
+        root = next((r for r in roots if r.id == msg["root_id"]), None)
+        if root is None:
+            raise ValueError("Did not find serialized root node %d" % msg["root_id"])
+        return SPNModel(root, msg["feature_type"], msg["name"] or None)

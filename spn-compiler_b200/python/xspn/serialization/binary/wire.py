@@ -1,4 +1,4 @@
-"""Cap'n Proto encoder for xspn files, written against the reference's schema
+"""Cap'n Proto encoder and decoder for xspn files, written against the reference's schema
 (xspn/xspn/serialization/binary/capnproto/spflow.capnp:27-101) without pycapnp.
 
 The whole message is laid out in ONE segment in the standard unpacked stream framing
@@ -189,3 +189,169 @@ def _ranges(cnt):
 def _frame(W):
     hdr = np.array([0, len(W)], dtype="<u4").tobytes()
     return hdr + W.astype("<u8").tobytes()
+
+
+# ------------------------------------------------------------------------------------------------
+# Reader.  Accepts any framing a Cap'n Proto writer may produce for the schema: several segments,
+# far and double-far pointers, structs stored shorter than the schema (missing fields read as zero).
+# ------------------------------------------------------------------------------------------------
+import struct as _st
+
+
+class _View:
+    """The segments of one unpacked Cap'n Proto stream message."""
+
+    def __init__(self, data):
+        self.data = bytes(data)
+        if len(self.data) < 8:
+            raise ValueError("not an xspn file: shorter than a segment table")
+        nseg = _st.unpack_from("<I", self.data, 0)[0] + 1
+        if nseg > 4096 or 4 + 4 * nseg > len(self.data):
+            raise ValueError("not an xspn file: bad segment count")
+        words = _st.unpack_from("<%dI" % nseg, self.data, 4)
+        at = (4 + 4 * nseg + 7) & ~7
+        self.start, self.words = [], list(words)
+        for w in words:
+            self.start.append(at)
+            at += 8 * w
+        if at > len(self.data):
+            raise ValueError("xspn file truncated")
+
+    def u64(self, seg, w):
+        if not (0 <= seg < len(self.words)) or not (0 <= w < self.words[seg]):
+            raise ValueError("pointer leaves its segment")
+        return _st.unpack_from("<Q", self.data, self.start[seg] + 8 * w)[0]
+
+    def follow(self, seg, w):
+        """Pointer at (seg, w) -> (seg, pointer value describing the object, first content word) or None."""
+        p = self.u64(seg, w)
+        if p == 0:
+            return None
+        if p & 3 != 2:
+            off = (p >> 2) & 0x3FFFFFFF
+            off -= (off & (1 << 29)) << 1
+            return seg, p, w + 1 + off
+        pad_seg, pad = p >> 32, (p >> 3) & 0x1FFFFFFF
+        if not (p >> 2) & 1:
+            return self.follow_pad(pad_seg, pad)
+        far, tag = self.u64(pad_seg, pad), self.u64(pad_seg, pad + 1)
+        if far & 3 != 2:
+            raise ValueError("malformed double-far pointer")
+        return far >> 32, tag, (far >> 3) & 0x1FFFFFFF
+
+    def follow_pad(self, seg, w):
+        r = self.follow(seg, w)
+        if r is None or self.u64(seg, w) & 3 == 2:
+            raise ValueError("malformed far pointer")
+        return r
+
+
+class _Rec:
+    """One struct: `dw` data words followed by `pw` pointers."""
+
+    def __init__(self, view, seg, w, dw, pw):
+        self.v, self.seg, self.w, self.dw, self.pw = view, seg, w, dw, pw
+        if w < 0 or w + dw + pw > view.words[seg]:
+            raise ValueError("struct leaves its segment")
+
+    def scalar(self, fmt, byte):
+        size = _st.calcsize(fmt)
+        if byte + size > 8 * self.dw:
+            return 0
+        return _st.unpack_from(fmt, self.v.data, self.v.start[self.seg] + 8 * self.w + byte)[0]
+
+    def _target(self, i):
+        return None if i >= self.pw else self.v.follow(self.seg, self.w + self.dw + i)
+
+    def child(self, i):
+        t = self._target(i)
+        if t is None:
+            return None
+        seg, p, w = t
+        if p & 3 != 0:
+            raise ValueError("expected a struct pointer")
+        return _Rec(self.v, seg, w, (p >> 32) & 0xFFFF, (p >> 48) & 0xFFFF)
+
+    def array(self, i, dtype):
+        t = self._target(i)
+        if t is None:
+            return np.zeros(0, dtype)
+        seg, p, w = t
+        size_code = {1: 2, 2: 3, 4: 4, 8: 5}[np.dtype(dtype).itemsize]
+        if p & 3 != 1 or (p >> 32) & 7 != size_code:
+            raise ValueError("expected a list of %s" % np.dtype(dtype).name)
+        count = p >> 35
+        if 8 * w + count * np.dtype(dtype).itemsize > 8 * self.v.words[seg] or w < 0:
+            raise ValueError("list leaves its segment")
+        return np.frombuffer(self.v.data, np.dtype(dtype).newbyteorder("<"), count, self.v.start[seg] + 8 * w).astype(dtype)
+
+    def text(self, i):
+        b = self.array(i, np.uint8)
+        return bytes(b[:-1]).decode("utf-8") if len(b) else ""
+
+    def records(self, i):
+        t = self._target(i)
+        if t is None:
+            return []
+        seg, p, w = t
+        if p & 3 != 1 or (p >> 32) & 7 != 7:
+            raise ValueError("expected a list of structs")
+        tag = self.v.u64(seg, w)
+        count, dw, pw = (tag >> 2) & 0x3FFFFFFF, (tag >> 32) & 0xFFFF, (tag >> 48) & 0xFFFF
+        return [_Rec(self.v, seg, w + 1 + k * (dw + pw), dw, pw) for k in range(count)]
+
+
+def decode_message(data):
+    """Decode an xspn file (bytes) into plain Python data:
+    {"query": None | {batch_size, error_kind, max_error, support_marginal}, "root_id", "num_features", "name",
+     "feature_type", "scope": [...], "nodes": [{"id", "root", "kind", ...kind-specific fields...}]}.
+    Field positions follow spflow.capnp:27-101 of the reference."""
+    view = _View(data)
+    t = view.follow(0, 0)
+    if t is None or t[1] & 3 != 0:
+        raise ValueError("xspn file has no header struct")
+    header = _Rec(view, t[0], t[2], (t[1] >> 32) & 0xFFFF, (t[1] >> 48) & 0xFFFF)
+    out = {"query": None}
+    which = header.scalar("<H", 0)
+    if which == 1:
+        q = header.child(0)
+        if q is None:
+            raise ValueError("query header without a query")
+        joint = q.child(0)
+        if joint is None:
+            raise ValueError("Can only deserialize joint queries")
+        out["query"] = {"batch_size": q.scalar("<i", 0), "error_kind": q.scalar("<H", 4), "max_error": float(q.scalar("<d", 8)),
+                        "support_marginal": bool(joint.scalar("<B", 0) & 1)}
+        model = joint.child(0)
+    elif which == 0:
+        model = header.child(0)
+    else:
+        raise NotImplementedError("No deserialization defined for header content %d" % which)
+    if model is None:
+        raise ValueError("No model attached")
+    out.update(root_id=model.scalar("<i", 0), num_features=model.scalar("<I", 4), name=model.text(0),
+               feature_type=model.text(1), scope=[int(s) for s in model.array(2, np.int32)], nodes=[])
+    for rec in model.records(3):
+        kind = rec.scalar("<H", 6)
+        node = {"id": rec.scalar("<i", 0), "root": bool(rec.scalar("<B", 4) & 1), "kind": kind}
+        body = rec.child(0)
+        if body is None:
+            raise ValueError("node %d has no content" % node["id"])
+        if kind == K_PRODUCT:
+            node["children"] = [int(c) for c in body.array(0, np.int32)]
+        elif kind == K_SUM:
+            node["children"] = [int(c) for c in body.array(0, np.int32)]
+            node["weights"] = [float(w) for w in body.array(1, np.float64)]
+        elif kind == K_HIST:
+            node.update(type=body.scalar("<H", 0), meta_type=body.scalar("<H", 2), scope=body.scalar("<i", 4),
+                        breaks=[int(b) for b in body.array(0, np.int32)],
+                        densities=[float(d) for d in body.array(1, np.float64)],
+                        bin_repr_points=[float(r) for r in body.array(2, np.float64)])
+        elif kind == K_GAUSS:
+            node.update(mean=float(body.scalar("<d", 0)), stddev=float(body.scalar("<d", 8)), scope=body.scalar("<i", 16))
+        elif kind == K_CAT:
+            node.update(scope=body.scalar("<i", 0), probabilities=[float(p) for p in body.array(0, np.float64)])
+        else:
+            raise NotImplementedError("No deserialization defined for node kind %d" % kind)
+        out["nodes"].append(node)
+    return out

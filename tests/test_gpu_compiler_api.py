@@ -136,3 +136,25 @@ def test_sharded_entry_on_the_visible_devices(tmp_path):
     want = oracle.evaluate(oracle.load_model(q), x, "log_f64")
     assert max_rel_err(out, want) <= REL_TOL_F32
     assert abs(mean - want.mean()) <= 1e-4 * abs(want.mean())
+
+
+def test_partitioned_cuda_NIPS5(golden_dir):
+    """The reference's partitioned CUDA test (python-interface/test/examples/NIPS5/test_partitioned_cuda_NIPS5.py:24-42):
+    the stored NIPS5 query read back with BinaryDeserializer, compiled with computeInLogSpace=False and
+    maxTaskSize=10, i.e. cut into functions of at most ten nodes whose results travel through global scratch."""
+    from spnc.gpu import CUDACompiler
+    from xspn.serialization.binary.BinarySerialization import BinaryDeserializer
+    query = BinaryDeserializer(os.path.join(golden_dir, "NIPS5.bin")).deserialize_from_file()
+    spn = query.graph.root
+    z = np.load(os.path.join(golden_dir, "NIPS5_io.npz"))
+    inputs, reference = z["inputs"].astype(np.int32), z["outputs"].reshape(-1)
+    results = CUDACompiler(computeInLogSpace=False, maxTaskSize=10).log_likelihood(spn, inputs, supportMarginal=False)
+    assert results.dtype == np.float64
+    assert np.all(np.isclose(results, reference)) or np.all(np.isclose(np.exp(results), np.exp(reference)))
+    # the option really partitions: the generated source passes values through the scratch area
+    kernel = CUDACompiler(computeInLogSpace=False, maxTaskSize=10).compile_ll(spn, "int32", supportMarginal=False)
+    from spnb import capi
+    plan = capi.Plan(kernel.fileName())
+    assert plan.stats["scratch_slots"] > 0 and "st.global" in plan.source
+    plan.close()
+    os.remove(kernel.fileName())

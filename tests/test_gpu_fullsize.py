@@ -1,8 +1,10 @@
 """Properties checked at the full BASELINE batch sizes, where the oracle would take too long to evaluate
-everything: (1) a random 20 000-sample subset agrees with the oracle; (2) the result does not depend on
+everything: (1) a random subset agrees with the oracle; (2) the result does not depend on
 how the batch is cut (whole batch through the device entry = two halves = host-path chunks = sharded);
 (3) marginalising a feature can only raise the likelihood of a sample (log-space monotonicity) and
-marginalising everything gives log 1 = 0."""
+marginalising everything gives log 1 = 0.  The two largest configurations (the 53 k-node DAG and the
+662 k-node layered model) are additionally compared with the reference-order f32 oracle, and the layered
+tensor-core result with the scalar layered kernel."""
 import numpy as np
 import pytest
 
@@ -73,4 +75,83 @@ def test_layered_batch_larger_than_one_transposition_chunk(tmp_path):
     cut = 524288 + 333
     assert np.array_equal(np.concatenate([_device_run(plan, x, 0, cut), _device_run(plan, x, cut, n)]), whole)
     assert np.array_equal(plan.execute_host(x), whole)
+    plan.close()
+
+
+def _subset_check(q, x, idx, got, chunk):
+    """`got` (device results of rows idx) against the f64 oracle and the reference-order f32 oracle."""
+    from oracle import oracle
+    m = oracle.load_model(q)
+    sub = np.ascontiguousarray(x[idx])
+    for mode in ("log_f64", "log_f32_gpu"):
+        want = oracle.evaluate(m, sub, mode, chunk=chunk)
+        err = max_rel_err(got, want)
+        assert err <= REL_TOL_F32, (mode, err)
+
+
+def test_full_batch_config4_mixed_dag(tmp_path):
+    """BASELINE configuration 4 at full size: ~53 k nodes over 128 Gaussian + 128 categorical features, default
+    options (chunked generated kernel, values crossing chunks through per-CTA scratch), 4 M samples."""
+    from spnb import capi, synth
+    spn = synth.config4()
+    q = write_query(spn, True, directory=str(tmp_path))
+    plan_path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true"})
+    plan = capi.Plan(plan_path)
+    assert plan.stats["nodes"] > 40000
+    n = 4_000_000
+    x = synth.config4_inputs(n)
+    whole = _device_run(plan, x)
+    plan.device_status(0)
+    assert whole.shape == (n,) and np.isfinite(whole).all()
+    idx = np.sort(np.random.default_rng(8).choice(n, 6000, replace=False))
+    _subset_check(q, x, idx, whole[idx], 256)
+    cut = n // 2 + 4321
+    assert np.array_equal(np.concatenate([_device_run(plan, x, 0, cut), _device_run(plan, x, cut, n)]), whole)
+    # missing values: Gaussian and categorical columns of a slice marginalised, checked against the oracle
+    sub = x[:100000].copy()
+    sub[::3, 5] = np.nan
+    sub[::4, 200] = np.nan
+    got = _device_run(plan, sub)
+    pick = np.arange(0, 100000, 50)
+    assert max_rel_err(got[pick], oracle_eval(q, sub[pick], True)) <= REL_TOL_F32
+    sub[:] = np.nan
+    assert np.abs(_device_run(plan, sub[:4096])).max() <= 1e-4
+    plan.close()
+
+
+def test_full_batch_config5_layered(tmp_path):
+    """BASELINE configuration 5 at full size: 784 features, depth 4, 16 repetitions, 32 x 1024 dense sums
+    (662 529 nodes), 2 M samples on the tensor-core layered kernel; a subset against both oracles and against
+    the scalar layered kernel, and the bounded-wait status of the device afterwards."""
+    from spnb import capi, synth
+    spn = synth.config5()
+    q = write_query(spn, True, directory=str(tmp_path))
+    plan_path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true"})
+    plan = capi.Plan(plan_path)
+    assert plan.stats["strategy"] == "layered" and plan.stats["nodes"] > 600000
+    n = 2_000_000
+    x = synth.config5_inputs(n)
+    whole = _device_run(plan, x)
+    plan.device_status(0)
+    assert whole.shape == (n,) and np.isfinite(whole).all()
+    idx = np.sort(np.random.default_rng(9).choice(n, 5000, replace=False))
+    _subset_check(q, x, idx, whole[idx], 32)
+    scalar_path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "layered-scalar"})
+    scalar = capi.Plan(scalar_path)
+    sub = np.ascontiguousarray(x[idx])
+    assert max_rel_err(whole[idx], scalar.execute_host(sub)) <= REL_TOL_F32
+    scalar.close()
+    cut = 3 * 524288 + 777   # inside the last 512 Ki-sample transposition chunk
+    assert np.array_equal(np.concatenate([_device_run(plan, x, 0, cut), _device_run(plan, x, cut, n)]), whole)
+    plan.device_status(0)
+    # missing values in a slice
+    part = x[:65536].copy()
+    part[::5, 100] = np.nan
+    part[7, :] = np.nan
+    got = _device_run(plan, part)
+    assert abs(got[7]) <= 1e-4
+    pick = np.arange(0, 65536, 128)
+    from oracle import oracle
+    want = oracle.evaluate(oracle.load_model(q), np.ascontiguousarray(part[pick]), "log_f64", chunk=32)
+    assert max_rel_err(got[pick], want) <= REL_TOL_F32
     plan.close()

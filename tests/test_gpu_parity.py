@@ -161,6 +161,42 @@ def test_layered_ratspn_kernel(capi, tmp_path):
         capi.compile_query(q, _opts(True, spnb_kernel="layered"))
 
 
+def test_layered_kernels_with_raw_scale_gaussians(capi, tmp_path):
+    """Leaf means hundreds of standard deviations away from zero and from each other (pixel-scale data with
+    narrow components): every layered kernel must evaluate c2 (x - mu)^2 + c1 in the centred form, an expanded
+    quadratic loses whole units per leaf here.  Inputs sit near one component's means, so that the
+    log-likelihood is moderate and the relative tolerance is a tight absolute one."""
+    from spnb import synth
+    from xspn.serialization.binary import wire
+    spn = synth.config5(seed=23, num_features=64, depth=2, repetitions=2, width=32, mean_dist=(120.0, 40.0), sd_range=(0.05, 0.12))
+    q = write_query(spn, True, directory=str(tmp_path))
+    a = spn.a
+    g = np.nonzero(a["kind"] == wire.K_GAUSS)[0]
+    first = {}
+    for i in g:                       # the first Gaussian listed for each feature (repetition 0, component 0)
+        first.setdefault(int(a["scope_id"][i]), i)
+    mu = np.array([a["mean"][first[f]] for f in range(64)])
+    sd = np.array([a["stddev"][first[f]] for f in range(64)])
+    rng = np.random.default_rng(3)
+    n = 4097
+    x = (mu[None, :] + rng.standard_normal((n, 64)) * sd[None, :]).astype(np.float32)
+    x[::9, 4] = np.nan
+    want = oracle_eval(q, x, True)
+    assert np.isfinite(want).all() and np.abs(want).max() < 2000.0
+    # float32 inputs near 120 carry 4e-6 of rounding into differences of the order of 0.1: the reference's own
+    # f32 arithmetic (restated by the oracle's log_f32_gpu mode) is a few 1e-5 away from the f64 value here.
+    # The kernels must be as close as that arithmetic allows; the expanded quadratic would be off by 1e-2.
+    inherent = max_rel_err(oracle_eval(q, x, True, "log_f32_gpu"), want)
+    assert inherent < 2e-4
+    for mode in ("layered", "layered-mma", "layered-scalar", "interp"):
+        path, _ = capi.compile_query(q, _opts(True, spnb_kernel=mode))
+        plan = capi.Plan(path)
+        err = max_rel_err(plan.execute_host(x), want)
+        assert err <= max(REL_TOL_F32, 4.0 * inherent), (mode, err, inherent)
+        plan.close()
+        os.remove(path)
+
+
 def test_streamed_table_window(capi, tmp_path):
     """Leaf tables larger than the shared-memory window are reloaded piecewise inside the kernel body."""
     for idx in (3, 4, 1):
