@@ -222,6 +222,13 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
       o.tcWarpgroups = std::atoi(v.c_str());
       if (o.tcWarpgroups != 1 && o.tcWarpgroups != 2 && o.tcWarpgroups != 4) fail("spnb-tc-warpgroups must be 1, 2 or 4");
     }
+    else if (k == "spnb-tc-tiles") {
+      o.tcTiles = std::atoi(v.c_str());
+      if (o.tcTiles != 1 && o.tcTiles != 2) fail("spnb-tc-tiles must be 1 or 2");
+    } else if (k == "spnb-spin-limit") {
+      o.spinLimit = std::atoll(v.c_str());
+      if (o.spinLimit < 0 || o.spinLimit > (1ll << 30)) fail("spnb-spin-limit must be between 0 and 2^30");
+    } else if (k == "spnb-selftest-withhold-commit") o.selftestWithhold = std::atoi(v.c_str());
     else if (!ignored.count(k)) fail("Unknown compile option " + k);
   }
   if (!haveTarget) fail("Missing required option target");
@@ -364,6 +371,13 @@ struct Engine::DeviceState {
   bool useTcf = false;
   void* dCentres = nullptr;
   void* dLeafCols = nullptr;
+  // two-tile tcgen05 kernel
+  bool useDual = false;
+  DualArgs da{};
+  void* dDualSteps = nullptr;
+  void* dDualCols = nullptr;
+  void* dDualCentres = nullptr;
+  int samplesPerCta = 0;     // samples one CTA takes per step of its tile loop, if not the block size
   size_t layeredChunkRows = 0;
   int* dStatus = nullptr;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
@@ -407,6 +421,9 @@ struct Engine::DeviceState {
     if (dStatus) cudaFree(dStatus);
     if (dCentres) cudaFree(dCentres);
     if (dLeafCols) cudaFree(dLeafCols);
+    if (dDualSteps) cudaFree(dDualSteps);
+    if (dDualCols) cudaFree(dDualCols);
+    if (dDualCentres) cudaFree(dDualCentres);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -444,6 +461,9 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->layeredScalar_ = opt.kernelMode == "layered-scalar";
   e->mmaSplit_ = opt.mmaSplit != 0;
   e->tcWarpgroups_ = opt.tcWarpgroups;
+  e->tcTiles_ = opt.tcTiles;
+  if (opt.spinLimit > 0) e->spinLimit_ = (unsigned)opt.spinLimit;
+  e->selftestWithhold_ = opt.selftestWithhold;
   // layered models run on the tensor-memory kernel unless another layered kernel is asked for by name
   e->layeredTcf_ = opt.kernelMode != "layered-scalar" && opt.kernelMode != "layered-mma";
   e->meta_.kernelName = e->model_.name;
@@ -453,6 +473,30 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->meta_.bytesPerResult = opt.logSpace ? 4 : 8;
   e->meta_.dtype = opt.logSpace ? "float32" : "float64";
   e->statsJson_ = makeStatsJson(e->plan_, e->strategy_, e->emitInfo_, regs, spill, e->plan_.numSlots);
+  if (e->strategy_ == kLayered && e->layeredTcf_) {
+    // would the two-tile tensor-core kernel take this model?  (judged from the region widths alone; leaf regions
+    // whose parameters leave half-precision range are decided when the plan is set up on a device)
+    LayeredPlan lp;
+    DualProgram prog;
+    bool dual = false;
+    if (opt.tcTiles == 2 && opt.tcWarpgroups == 1 && recogniseLayers(e->plan_.dag, &lp)) {
+      const size_t ns = lp.steps.size();
+      std::vector<long long> frag(ns, 0);
+      std::vector<int> blocks(ns, 0), scaleOff(ns, 0);
+      for (size_t i = 0; i < ns; ++i) {
+        const LayerStep& s = lp.steps[i];
+        if (s.op != kLeafRegion) {
+          frag[i] = (s.wa == 32 && s.wb == 32 && s.width <= 32) ? 0 : -1;
+          blocks[i] = (s.width * 32 + 127) / 128;
+        }
+      }
+      dual = buildDualProgram(lp, frag, blocks, scaleOff, std::vector<float>(lp.features.size(), 0.f), &prog);
+    }
+    e->statsJson_.pop_back();
+    e->statsJson_ += std::string(",\"tc_tiles\":") + (dual ? "2" : "1");
+    if (dual) e->statsJson_ += ",\"tc_program\":" + dualProgramSummary(prog);
+    e->statsJson_ += "}";
+  }
   return e;
 }
 
@@ -696,6 +740,56 @@ Engine::DeviceState& Engine::state(int device) {
         st->la.warpgroups = tcWarpgroups_;
         CUDA_OK(cudaMalloc(&st->dStatus, sizeof(int)));
         CUDA_OK(cudaMemset(st->dStatus, 0, sizeof(int)));
+        // ---- two tiles per CTA, if the program fits that kernel's constraints ----------------------------
+        if (tcTiles_ == 2 && tcWarpgroups_ == 1) {
+          DualProgram prog;
+          std::vector<long long> fragOffsets(steps.size());
+          std::vector<int> blockCounts(steps.size()), scaleOffsets(steps.size());
+          for (size_t i = 0; i < steps.size(); ++i) {
+            fragOffsets[i] = mma[i].fragOffset;
+            blockCounts[i] = mma[i].numTiles;
+            scaleOffsets[i] = mma[i].scaleOffset;
+          }
+          if (buildDualProgram(lp, fragOffsets, blockCounts, scaleOffsets, centres, &prog)) {
+            std::vector<DualStepDev>& ds = prog.steps;
+            std::vector<int>& cols4 = prog.cols4;
+            std::vector<float>& centres4 = prog.centres4;
+            const size_t ns = ds.size();
+            const int maxDepth = prog.aSlots, depth = 0;
+            int ring = 0;
+            for (int cand : {4, 3})
+              if (!ring && layeredDualSmemBytes(std::max(maxDepth, 1), cand) <= (size_t)prop.sharedMemPerBlockOptin) ring = cand;
+            if (ring && depth == 0) {
+              if (cols4.empty()) { cols4.assign(4, 0); centres4.assign(4, 0.f); }
+              st->dDualSteps = upload(ds.data(), ds.size() * sizeof(DualStepDev));
+              st->dDualCols = upload(cols4.data(), cols4.size() * 4);
+              st->dDualCentres = upload(centres4.data(), centres4.size() * 4);
+              st->da.steps = (const DualStepDev*)st->dDualSteps;
+              st->da.numSteps = (int)ns;
+              st->da.aSlots = std::max(maxDepth, 1);
+              st->da.ringBlocks = ring;
+              st->da.marginal = st->la.marginal;
+              st->da.frags = (const unsigned char*)st->dFrags;
+              st->da.scales = (const float*)st->dScales;
+              st->da.leafCols = (const int*)st->dDualCols;
+              st->da.leafCentres = (const float*)st->dDualCentres;
+              st->da.numLeafStages = (int)(cols4.size() / 4);
+              st->da.features = st->la.features;
+              st->da.leafParams = st->la.leafParams;
+              st->da.spinLimit = spinLimit_;
+              st->da.testWithholdCommit = selftestWithhold_;
+              st->useDual = true;
+              st->block = layeredDualThreads();
+              st->samplesPerCta = 256;
+              st->smem = layeredDualSmemBytes(st->da.aSlots, ring);
+              st->grid = st->smCount;   // one CTA per SM: the kernel owns the SM's tensor memory
+              st->layeredChunkRows = 512 * 1024;
+              st->scratchBytes = st->layeredChunkRows * (size_t)p.features.size() * 4;
+              auto insD = dev_.emplace(device, std::move(st));
+              return *insD.first->second;
+            }
+          }
+        }
         st->block = 128;
         st->smem = layeredTcfSmemBytes(st->la);
         if (st->smem > (size_t)prop.sharedMemPerBlockOptin) fail("Layered tcgen05 kernel: region stack too deep for shared memory");
@@ -839,9 +933,14 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
       CUDA_OK(transposeInputs(dtypeCode(plan_.ftype), src, xt, rows, (int)meta_.numFeatures, ld, stream));
       LayeredArgs la = st.la;
       la.xtLd = (long long)ld;
-      const size_t tilesC = (rows + (size_t)st.block - 1) / (size_t)st.block;
+      const size_t perCta = st.samplesPerCta ? (size_t)st.samplesPerCta : (size_t)st.block;
+      const size_t tilesC = (rows + perCta - 1) / perCta;
       const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);
-      if (st.useTcf) CUDA_OK(layeredTcfLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
+      if (st.useDual) {
+        DualArgs da = st.da;
+        da.xtLd = (long long)ld;
+        CUDA_OK(layeredDualLaunch(da, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
+      } else if (st.useTcf) CUDA_OK(layeredTcfLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
       else if (st.useMma) CUDA_OK(layeredMmaLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, stream));
       else CUDA_OK(layeredLaunch(la, DT_F32, xt, dst, rows, gridC, st.block, st.smem, stream));
     }

@@ -41,6 +41,10 @@ struct Options {
   int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
   int mmaSplit = 1;            // "spnb-mma-split": 1 = half-precision operands carry their rounding residue (3 MMAs), 0 = plain fp16
   int tcWarpgroups = 1;        // "spnb-tc-warpgroups": warpgroups (128 threads) per CTA of the tensor-memory layered kernel
+  int tcTiles = 2;             // "spnb-tc-tiles": 2 = two sample tiles per CTA where the model allows it, 1 = one tile
+  long long spinLimit = 0;     // "spnb-spin-limit": polls after which a tensor-core barrier wait gives up (0 = 2^22)
+  int selftestWithhold = 0;    // "spnb-selftest-withhold-commit": 1 = the two-tile kernel leaves out one commit (tests
+                               // that a bounded wait runs out and is reported; results of such a plan are invalid)
   int bucketArith = 0;         // "spnb-bucket-arith": 1 = compute histogram buckets by multiply-shift where exact (measured slower: off)
   int interpSlots = 0;         // "spnb-interp-slots": cap on the interpreter's shared-memory value slots (0 = as many as fit)
   int groupTiles = 0;          // "spnb-group-tiles": tiles per chunk run of a chunked kernel (0 = automatic)
@@ -92,6 +96,9 @@ class Engine {
   bool layeredScalar_ = false;
   bool mmaSplit_ = true;
   int tcWarpgroups_ = 1;
+  int tcTiles_ = 2;
+  unsigned spinLimit_ = 1u << 22;
+  int selftestWithhold_ = 0;
   bool layeredTcf_ = false;
   std::string source_;
   std::vector<char> cubin_;

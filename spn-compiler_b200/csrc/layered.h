@@ -72,4 +72,74 @@ size_t layeredTcfSmemBytes(const LayeredArgs& a);
 cudaError_t layeredTcfLaunch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid,
                              size_t smem, int* status, cudaStream_t stream);
 
+// ---- tcgen05 / TMEM kernel with two sample tiles per CTA (layered_tcf_dual.cu) --------------------------------
+// Runs layered models whose inner regions are all full width (32 x 32 cross products, at most 32 sums) and
+// whose pending left operands fit into shared memory; everything else stays on layeredTcfKernel.
+// The region program is the same post-order walk, annotated with where every region's outputs go.
+enum DualDest : int {
+  kDualDestStack = 0,     // left operand of a later step: a-stack slot `destSlot` in shared memory
+  kDualDestOperand = 1,   // right operand of the next step: written as MMA operand rows
+  kDualDestRegs = 2,      // left operand of the step after next (its right sibling is one leaf region): registers
+  kDualDestRoot = 3       // root part: folded into the running root log-sum
+};
+
+struct DualStepDev {
+  int op;                 // LayerOp
+  int width;              // outputs
+  int dest, destSlot;     // DualDest
+  int aSrc;               // inner / root part: a-stack slot of the left operand, -1 = registers
+  int numBlocks;          // inner: blocks of 128 (k,i) columns; leaf: stages of four features (0: FP32 loop only)
+  long long fragOffset;   // byte offset of the step's weights in LayeredArgs::frags
+  int scaleOffset;        // inner: first of 32 per-sum log2 scales
+  int stageBase;          // leaf: first stage of the region in DualArgs::leafCols / leafCentres
+  int numFeatures, featOffset;   // leaf: FP32 path
+  long long paramOffset;  // leaf: first float4 of the region's (mu, c2, c1, 0) parameters
+};
+
+struct DualArgs {
+  const DualStepDev* steps;
+  int numSteps;
+  int aSlots;              // a-stack slots per tile
+  int ringBlocks;          // 16 KB weight blocks in flight (3 or 4)
+  int marginal;
+  const unsigned char* frags;   // same blocks as layeredTcfKernel reads
+  const float* scales;
+  const int* leafCols;          // per stage of four features (every region padded to a multiple of four stages):
+  const float* leafCentres;     //   input column (padding: 0) and the offset subtracted from the input
+  int numLeafStages;
+  const int* features;          // FP32 leaf path, as in LayeredArgs
+  const float4* leafParams;
+  long long xtLd;               // leading dimension of the feature-major input copy
+  unsigned spinLimit;           // polls after which a barrier wait gives up
+  int testWithholdCommit;       // self-test: the issuer leaves out one commit, so that a bounded wait runs out
+};
+
+size_t layeredDualSmemBytes(int aSlots, int ringBlocks);
+
+}  // namespace spnb
+
+#include <string>
+#include <vector>
+
+namespace spnb {
+
+struct LayeredPlan;
+struct DualProgram {
+  std::vector<DualStepDev> steps;
+  std::vector<int> cols4;        // DualArgs::leafCols
+  std::vector<float> centres4;   // DualArgs::leafCentres
+  int aSlots = 0;
+};
+// Annotates the region program for the two-tile kernel.  Per step of `lp`: fragOffset (in 8-byte units, < 0: the
+// step has no tensor-core weights), blocks (128-column blocks of an inner region) and scaleOffset as the
+// one-tile kernel uses them; centres per entry of lp.features.  False if the program does not fit the
+// kernel (an inner region without tensor weights, or a walk that is not a post-order of binary region trees).
+bool buildDualProgram(const LayeredPlan& lp, const std::vector<long long>& fragOffset, const std::vector<int>& blocks,
+                      const std::vector<int>& scaleOffset, const std::vector<float>& centres, DualProgram* out);
+// {"a_slots":..,"leaf_stages":..,"steps":"..."}: one token per step, for the plan statistics and the tests
+std::string dualProgramSummary(const DualProgram& p);
+int layeredDualThreads();
+cudaError_t layeredDualLaunch(const DualArgs& a, const float* xt, float* out, size_t n, int grid, size_t smem, int* status,
+                              cudaStream_t stream);
+
 }  // namespace spnb

@@ -59,6 +59,14 @@ def test_option_handling(tmp_path):
             "collect-graph-stats": "true", "graph-stats-file": str(tmp_path / "stats.json")}
     path, info = capi.compile_query(q, opts)
     assert os.path.isfile(path) and os.path.isfile(tmp_path / "stats.json")
+    import json
+    gs = json.load(open(tmp_path / "stats.json"))
+    # the reference's key set (LoSPNGraphStatsCollection.cpp:83-102) with the engine's own statistics beside it
+    for key in ("featureCount", "minDepth", "maxDepth", "averageDepth", "medianDepth", "innerCount", "leafCount",
+                "sumCount", "productCount", "categoricalCount", "constantCount", "gaussianCount", "histogramCount"):
+        assert key in gs, key
+    assert gs["featureCount"] == 16 and gs["gaussianCount"] == 0 and gs["categoricalCount"] == gs["spnb"]["categorical"]
+    assert gs["minDepth"] <= gs["medianDepth"] <= gs["maxDepth"] and gs["innerCount"] == gs["sumCount"] + gs["productCount"]
     assert info.dtype == b"float32" and info.bytes_per_result == 4 and info.query_type == 1 and info.target == 2
     path, info = capi.compile_query(q, {"target": "CUDA"})  # reference default: linear space, f64 result
     assert info.dtype == b"float64" and info.bytes_per_result == 8
@@ -177,3 +185,54 @@ def test_histogram_buckets_can_be_computed_where_that_is_exact(tmp_path):
                                     "spnb-bucket-arith": "1"})
     src2 = capi.Plan(p2).source
     assert src2.count(") >> 16;") == 1 and "lut_s" in src2
+
+
+def test_two_tile_tensor_core_program(tmp_path):
+    """The plan of a full-width layered model is annotated for the two-tile tensor-core kernel: right operands
+    go straight to the operand buffer, left operands wait in registers (sibling = one leaf region) or in an
+    a-stack whose depth is the region-tree depth minus one; narrower models stay on the one-tile kernel."""
+    from spnb import capi, synth
+    for depth in (1, 2, 3, 4):
+        spn = synth.config5(seed=3, num_features=16 * 2 ** depth, depth=depth, repetitions=2, width=32)
+        q = write_query(spn, True, directory=str(tmp_path))
+        path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "layered"})
+        st = capi.Plan(path).stats
+        assert st["tc_tiles"] == 2
+        prog = st["tc_program"]
+        assert prog["a_slots"] == max(depth - 1, 1)
+        steps = prog["steps"].split()
+        assert len(steps) == 2 * (2 ** (depth + 1) - 1)
+        # replay: slots are used as a stack, every inner step finds its operands where the program says
+        live, regs, operand = [], False, False
+        for tok in steps:
+            kind = tok[0]
+            if kind in "IR":
+                src = tok[1]
+                assert operand, tok
+                operand = False
+                if src == "r":
+                    assert regs
+                    regs = False
+                else:
+                    assert live and live[-1] == int(src), (tok, live)
+                    live.pop()
+            dest = tok[1:] if kind == "L" else tok[2:]
+            if dest == "o":
+                assert not operand
+                operand = True
+            elif dest == "r":
+                assert not regs
+                regs = True
+            elif dest.startswith("s"):
+                assert int(dest[1:]) == len(live)
+                live.append(int(dest[1:]))
+            else:
+                assert dest == "-" and kind == "R"
+        assert not live and not regs and not operand
+    narrow = synth.config5(seed=3, num_features=32, depth=2, repetitions=2, width=8)
+    q = write_query(narrow, True, directory=str(tmp_path))
+    path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "layered"})
+    assert capi.Plan(path).stats["tc_tiles"] == 1
+    path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "layered", "spnb-tc-tiles": "1"})
+    with pytest.raises(capi.SpnbError, match="spnb-tc-tiles"):
+        capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-tc-tiles": "3"})

@@ -137,6 +137,11 @@ def test_layered_ratspn_kernel(capi, tmp_path):
             path, _ = capi.compile_query(q, _opts(True, spnb_kernel=mode))
             plans[mode] = (capi.Plan(path), path)
         if sh["width"] == 32:
+            # default: two sample tiles per CTA; the one-tile kernel by name and with more warpgroups
+            assert plans["layered"][0].stats["tc_tiles"] == 2
+            path, _ = capi.compile_query(q, _opts(True, spnb_kernel="layered", spnb_tc_tiles=1))
+            plans["layered/1 tile"] = (capi.Plan(path), path)
+            assert plans["layered/1 tile"][0].stats["tc_tiles"] == 1
             for wgs in (2, 4):
                 path, _ = capi.compile_query(q, _opts(True, spnb_kernel="layered", spnb_tc_warpgroups=wgs))
                 plans["layered/%d warpgroups" % wgs] = (capi.Plan(path), path)
@@ -195,6 +200,37 @@ def test_layered_kernels_with_raw_scale_gaussians(capi, tmp_path):
         assert err <= max(REL_TOL_F32, 4.0 * inherent), (mode, err, inherent)
         plan.close()
         os.remove(path)
+
+
+def test_bounded_wait_runs_out_and_is_reported(capi, tmp_path):
+    """The tensor-core kernels poll their barriers a limited number of times.  A plan compiled with the
+    self-test option makes the two-tile kernel leave out one commit; the waiting threads give up, the kernel
+    frees its tensor memory and returns normally, spnb_device_status reports the flag (and clears it), the host
+    entry point reports it too, and the device keeps working for other plans."""
+    import torch
+    from spnb import synth
+    spn = synth.config5(seed=5, num_features=64, depth=2, repetitions=2, width=32)
+    q = write_query(spn, True, directory=str(tmp_path))
+    x = synth.config5_inputs(4000, 3, num_features=64)
+    good_path, _ = capi.compile_query(q, _opts(True))
+    good = capi.Plan(good_path)
+    want = good.execute_host(x)
+    bad_path, _ = capi.compile_query(q, _opts(True, spnb_selftest_withhold_commit=1, spnb_spin_limit=20000))
+    bad = capi.Plan(bad_path)
+    assert bad.stats["tc_tiles"] == 2
+    dx = torch.from_numpy(x).cuda()
+    dout = torch.zeros(x.shape[0], dtype=torch.float32, device="cuda")
+    bad.execute_device(0, x.shape[0], dx.data_ptr(), dout.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    with pytest.raises(capi.SpnbError, match="bounded wait"):
+        bad.device_status(0)
+    bad.device_status(0)    # the flag was cleared by the report
+    with pytest.raises(capi.SpnbError, match="bounded wait"):
+        bad.execute_host(x)
+    bad.close()
+    # the context is intact: the regular plan still gives the same answers
+    assert np.array_equal(good.execute_host(x), want)
+    assert max_rel_err(want, oracle_eval(q, x, True)) <= REL_TOL_F32
+    good.close()
 
 
 def test_streamed_table_window(capi, tmp_path):
