@@ -109,7 +109,20 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   } else if (minBlocks <= 0) {
     minBlocks = std::max(1, 1024 / TILE);
   }
-  const int SX = TILE + 1;
+  // ---- scope-local staging (see EmitOptions::scoped) ---------------------------------------------------
+  // DAGs up to one and a half chunk sizes stay in one function; larger ones are cut into equal stretches
+  size_t chunkNodes = opt.chunkNodes > 0 ? (size_t)opt.chunkNodes : n;
+  if (n <= chunkNodes + chunkNodes / 2) chunkNodes = n;
+  else chunkNodes = (n + (n + chunkNodes - 1) / chunkNodes - 1) / ((n + chunkNodes - 1) / chunkNodes);
+  const bool scopedPossible = lg && p.ftype.isFloat() && p.ftype.bits == 32 && opt.groupTiles <= 1;
+  const bool scoped = scopedPossible &&
+                      (opt.scoped == 1 || (opt.scoped < 0 && opt.tile <= 0 && TILE < 1024 && n > chunkNodes));
+  if (scoped) {
+    TILE = opt.tile > 0 ? opt.tile : 1024;
+    minBlocks = 1;
+    tableLimit = std::min<size_t>((size_t)opt.smemTableLimit, 32 * 1024);
+  }
+  const int SX = scoped ? TILE : TILE + 1;   // the transposing store of the row-major path needs the padding
   // Leaf tables are always read from shared memory.  Tables larger than the window are streamed
   // through it: leaves appear in the body in table order, so at the points where the next leaf's
   // table lies beyond the window the CTA reloads the window from global memory between two barriers.
@@ -119,10 +132,85 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const bool floatIn = p.ftype.isFloat();
   const double LOG2E = 1.4426950408889634074;
   const int NV = p.numValueSlots, NC = p.numCodeSlots;
-  bool identity = (NC == 0 && NV == F);
+  bool identity = (NC == 0 && NV == F) && !scoped;
   for (int f = 0; identity && f < F; ++f) identity = p.features[f].valueSlot == f;
   const size_t lutBytes = lutBytesNeeded(p, opt);
   const bool lutSmem = lutBytes > 0 && lutBytes <= (size_t)opt.smemTableLimit;
+  // ---- asynchronous double-buffered staging (see EmitOptions::asyncStage) -----------------------------------
+  const int RS = F | 1;                                      // row stride in words: odd, conflict-free
+  const size_t asyncBuf = ((size_t)TILE * RS * 4 + 15) & ~size_t(15);
+  // every input is read as a value by Gaussian leaves (no staged codes, no leaf tables): the body indexes a
+  // staged row by the feature itself
+  const bool asyncStage = opt.asyncStage != 0 && !scoped && NC == 0 && NV > 0 && tabEntries == 0 && lg && floatIn &&
+                          p.ftype.bits == 32 && opt.groupTiles <= 1 && 2 * asyncBuf + 64 <= 226 * 1024;
+  const bool nanFlagsWanted = p.marginal && floatIn && NV > 0 && p.stats.gauss > 0;
+
+  // ---- chunks: consecutive stretches of the evaluation order, one generated function each -----------------
+  // Row-major path: equal stretches of chunkNodes nodes, every chunk reads the tile's inputs staged once.
+  // Scoped path: a stretch also ends where its leaves would need more staged bytes per sample than fit.
+  std::vector<size_t> chunkStart{0};
+  std::vector<int32_t> chunkOf(n, 0);
+  // per chunk: staged features (values, then codes) and, per node, the slot its leaf reads
+  std::vector<std::vector<int32_t>> chunkValueFeat, chunkCodeFeat;
+  std::vector<int32_t> leafSlot(n, -1);
+  size_t scopeBudget = 0, maxStageBytes = 0;
+  if (!scoped) {
+    for (size_t v = chunkNodes; v < n; v += chunkNodes) chunkStart.push_back(v);
+    for (size_t v = 0; v < n; ++v) chunkOf[v] = (int32_t)(v / chunkNodes);
+  } else {
+    const size_t fixed = 64 + std::min(tabBytes, tableLimit) + 16 + (lutSmem ? p.lut.size() + 4 : 0);
+    scopeBudget = (226 * 1024 - fixed) / (size_t)TILE - (nanFlagsWanted ? 4 : 0);
+    if (opt.scopeBytes > 0) scopeBudget = std::min<size_t>(scopeBudget, (size_t)opt.scopeBytes);
+    std::vector<int32_t> vstamp(F, -1), cstamp(F, -1), vslotOf(F, -1), cslotOf(F, -1);
+    chunkValueFeat.emplace_back();
+    chunkCodeFeat.emplace_back();
+    int32_t cur = 0;
+    size_t bytes = 0;
+    for (size_t v = 0; v < n; ++v) {
+      int32_t needValue = -1, needCode = -1;
+      if (d.kind[v] == kGaussian) needValue = d.feature[v];
+      else if (d.kind[v] == kCategorical || d.kind[v] == kHistogram) {
+        const IndexGroup& G = p.groups[d.group[v]];
+        if (G.mode == kGeneric) needValue = G.feature; else needCode = G.feature;
+      }
+      size_t add = 0;
+      if (needValue >= 0 && vstamp[needValue] != cur) add = 4;
+      if (needCode >= 0 && cstamp[needCode] != cur) add = (size_t)cb;
+      if (add > scopeBudget) add = scopeBudget;   // a budget smaller than one feature still makes progress
+      if ((bytes + add > scopeBudget && bytes > 0) || v - chunkStart.back() >= chunkNodes) {
+        chunkStart.push_back(v);
+        chunkValueFeat.emplace_back();
+        chunkCodeFeat.emplace_back();
+        ++cur;
+        bytes = 0;
+      }
+      chunkOf[v] = cur;
+      if (needValue >= 0) {
+        if (vstamp[needValue] != cur) {
+          vstamp[needValue] = cur;
+          vslotOf[needValue] = (int32_t)chunkValueFeat.back().size();
+          chunkValueFeat.back().push_back(needValue);
+          bytes += 4;
+        }
+        leafSlot[v] = vslotOf[needValue];
+      }
+      if (needCode >= 0) {
+        if (cstamp[needCode] != cur) {
+          cstamp[needCode] = cur;
+          cslotOf[needCode] = (int32_t)chunkCodeFeat.back().size();
+          chunkCodeFeat.back().push_back(needCode);
+          bytes += (size_t)cb;
+        }
+        leafSlot[v] = cslotOf[needCode];
+      }
+    }
+    for (size_t c = 0; c < chunkValueFeat.size(); ++c)
+      maxStageBytes = std::max(maxStageBytes, chunkValueFeat[c].size() * 4 + chunkCodeFeat[c].size() * (size_t)cb);
+  }
+  chunkStart.push_back(n);
+  const size_t nChunks = chunkStart.size() - 1;
+  // byte offset of a chunk's staged codes behind its staged values (scoped path)
+  auto codeBase = [&](size_t c) { return chunkValueFeat[c].size() * (size_t)4 * SX; };
   // Gaussian leaves of a query with marginal support must turn a NaN input into log 1 = 0: a compare
   // and a select per leaf.  NaNs are rare in practice, so the body is emitted twice: a plain version
   // and a NaN-aware one; a CTA takes the second only if one of its samples has a NaN among the staged
@@ -131,12 +219,13 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
 
   // shared memory layout (bytes): [fm int4 x NF] [xs real x NV*SX] [cs u8|u16 x NC*SX] [tab] [lut] [nan flags int x TILE]
   const size_t offFm = 0;
-  const size_t offXs = identity ? 0 : (size_t)F * 16;
+  const size_t offXs = (identity || scoped) ? 0 : (size_t)F * 16;
   const size_t offCs = offXs + (size_t)NV * SX * realBytes;
-  const size_t offTab = (offCs + (size_t)NC * SX * cb + 15) & ~size_t(15);
+  const size_t offTab = asyncStage ? 2 * asyncBuf
+                        : scoped ? ((maxStageBytes * SX + 15) & ~size_t(15)) : ((offCs + (size_t)NC * SX * cb + 15) & ~size_t(15));
   const size_t offLut = offTab + (tabSmem ? winBytes : 0);
   const size_t offNan = (offLut + (lutSmem ? p.lut.size() : 0) + 3) & ~size_t(3);
-  const size_t smemTotal = offNan + (twoBodies ? (size_t)TILE * 4 : 0);
+  const size_t smemTotal = offNan + ((twoBodies && !scoped && !asyncStage) ? (size_t)TILE * 4 : 0);
 
   std::ostringstream o;
   o << "// generated by spnb: straight-line joint log-likelihood kernel, one thread per sample\n";
@@ -171,7 +260,9 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const int rb = (int)realBytes;
   const char* ldReal = lg ? "ld.shared.f32" : "ld.shared.f64";
   const char* cReal = lg ? "f" : "d";
-  const bool mergeX = NV <= 32;  // few staged values (Gaussian inputs): identical reads may merge
+  size_t maxChunkValues = 0;
+  for (auto& cv : chunkValueFeat) maxChunkValues = std::max(maxChunkValues, cv.size());
+  const bool mergeX = scoped ? maxChunkValues <= 32 : NV <= 32;  // few staged values (Gaussian inputs): identical reads may merge
   auto ldsStmt = [&](const std::string& type, const char* inst, const char* constraint, const std::string& dst,
                      const std::string& base, long long imm, long long uniq) {
     std::ostringstream e;
@@ -181,7 +272,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     return e.str();
   };
   auto readX = [&](const std::string& dst, int slot, long long node) {
-    return ldsStmt("real_t", ldReal, cReal, dst, "xs_t", (long long)rb * slot * SX, mergeX ? -1 : node);
+    return ldsStmt("real_t", ldReal, cReal, dst, "xs_t", asyncStage ? (long long)rb * slot : (long long)rb * slot * SX, mergeX ? -1 : node);
   };
   auto readCode = [&](const std::string& dst, int slot, long long node) {
     return ldsStmt("int", cb == 1 ? "ld.shared.u8" : "ld.shared.u16", "r", dst, "cs_t", (long long)cb * slot * SX, node);
@@ -218,23 +309,25 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     const IndexGroup& G = p.groups[d.group[v]];
     const FeatureMeta& fm = p.features[G.feature];
     const std::string c = "c" + std::to_string(v);
+    const int codeSlot = scoped ? leafSlot[v] : fm.codeSlot;
+    const int valueSlot = scoped ? leafSlot[v] : (asyncStage ? G.feature : fm.valueSlot);
     if (G.mode == kDirect) {
-      out << readCode(c, fm.codeSlot, (long long)v) << readTab(name, p.tabOffset[v], c, (long long)v);
+      out << readCode(c, codeSlot, (long long)v) << readTab(name, p.tabOffset[v], c, (long long)v);
     } else if (G.mode == kLut && G.arith && opt.bucketArith) {
       // bucket computed from the code; codes 0 (missing input) and 1 (outside the domain) select the two
       // entries behind the buckets
       const std::string b = "b" + std::to_string(v);
-      out << readCode(c, fm.codeSlot, (long long)v);
+      out << readCode(c, codeSlot, (long long)v);
       out << "  const int " << b << " = " << c << " < 2 ? " << (G.count + 1) << " - " << c << " : (" << c << " * " << G.arMul
           << " + " << G.arAdd << ") >> 16;\n";
       out << readTab(name, p.tabOffset[v], b, (long long)v);
     } else if (G.mode == kLut) {
       const std::string b = "b" + std::to_string(v);
-      out << readCode(c, fm.codeSlot, (long long)v) << readLut(b, G.lutOffset, c, (long long)v)
+      out << readCode(c, codeSlot, (long long)v) << readLut(b, G.lutOffset, c, (long long)v)
           << readTab(name, p.tabOffset[v], b, (long long)v);
     } else {
       std::string xr = "xr" + std::to_string(v), xi = "xi" + std::to_string(v);
-      out << readX(xr, fm.valueSlot, (long long)v);
+      out << readX(xr, valueSlot, (long long)v);
       out << "  const int " << xi << " = " << (lg ? "__float2int_rz" : "__double2int_rz") << "(" << xr << ");\n";
       std::string cnt;
       for (int32_t i = 1; i < G.count; ++i) cnt += (i > 1 ? " + " : "") + std::string("(") + xi + " >= " + std::to_string(G.breaks[i]) + ")";
@@ -271,8 +364,6 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // the size of one function).  A value defined in one chunk and used in a later one travels through a
   // per-CTA scratch area in global memory, [slot][TILE] so that a warp's access is one 128-byte line;
   // slots are reused once their last consumer has run.
-  const size_t chunkNodes = opt.chunkNodes > 0 ? (size_t)opt.chunkNodes : n;
-  const size_t nChunks = (n + chunkNodes - 1) / chunkNodes;
   std::vector<int32_t> crossSlot(n, -1);
   int32_t nCross = 0;
   if (nChunks > 1) {
@@ -282,7 +373,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
         int32_t c = d.childIdx[e];
         lastUse[c] = std::max<int64_t>(lastUse[c], (int64_t)v);
-        if ((size_t)c / chunkNodes != v / chunkNodes) isCross[c] = 1;
+        if (chunkOf[c] != chunkOf[v]) isCross[c] = 1;
       }
     std::vector<std::vector<int32_t>> dying(n);
     for (size_t v = 0; v < n; ++v)
@@ -306,13 +397,16 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const char* stGlobal = lg ? "st.global.f32" : "st.global.f64";
   // ---- the DAG body: its own non-inlined function (the asm reads above must not move across the
   // barrier that follows the staging of a tile) ------------------------------------------------------
+  std::vector<long long> winEnd(nChunks, 0);
   auto emitBody = [&](const std::string& fname, bool nanAware, size_t chunk) {
-  const size_t v0 = chunk * chunkNodes, v1 = std::min(n, v0 + chunkNodes);
+  const size_t v0 = chunkStart[chunk], v1 = chunkStart[chunk + 1];
   o << "static __device__ __noinline__ out_t " << fname << "(const unsigned xs_s, const unsigned cs_s, const unsigned tab_s, "
        "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, uint4* __restrict__ win, "
        "real_t* __restrict__ sc, const unsigned tid)\n{\n";
-  o << "  const unsigned xs_t = xs_s + " << rb << "u * tid;\n  const unsigned cs_t = cs_s + " << cb << "u * tid;\n";
-  if (chunk == 0) winBase = 0;
+  o << "  const unsigned xs_t = xs_s + " << (asyncStage ? rb * RS : rb) << "u * tid;\n  const unsigned cs_t = cs_s + " << cb << "u * tid;\n";
+  // both variants of a chunk leave the same table window behind; a variant that skips a chunk (no staged
+  // values: nothing NaN-sensitive in it) continues from what the plain body of that chunk leaves
+  winBase = chunk == 0 ? 0 : winEnd[chunk - 1];
   // with grouped tiles a chunk runs several times in a row: it cannot rely on the window its predecessor left
   if (streamed && (chunk == 0 || groupTiles > 1)) swapWindow(o, winBase);
   std::vector<uint8_t> loaded(nChunks > 1 ? n : 0, 0);
@@ -334,7 +428,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       case kGaussian: {
         double sd = d.stddev[v];
         std::string x = "x" + std::to_string(v);
-        o << readX(x, p.features[d.feature[v]].valueSlot, (long long)v);
+        o << readX(x, scoped ? leafSlot[v] : (asyncStage ? d.feature[v] : p.features[d.feature[v]].valueSlot), (long long)v);
         if (lg) {
           float mu = (float)d.mean[v];
           float c2 = (float)(-(1.0 / (2.0 * sd * sd)) * LOG2E);
@@ -412,12 +506,176 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   if (v1 < n) o << "  return (out_t)0;\n}\n";
   else if (lg) o << "  return " << V(d.root()) << " * 0x1.62e43p-1f;\n}\n";  // log2 -> ln
   else o << "  return log(" << V(d.root()) << ");\n}\n";
+  winEnd[chunk] = winBase;
 
   };
   for (int variant = 0; variant < (twoBodies ? 2 : 1); ++variant)
-    for (size_t c = 0; c < nChunks; ++c)
+    for (size_t c = 0; c < nChunks; ++c) {
+      if (scoped && variant == 1 && chunkValueFeat[c].empty()) continue;
       emitBody(std::string(variant ? "spnb_body_nan" : "spnb_body") + std::to_string(c),
                twoBodies ? variant == 1 : (p.marginal && floatIn), c);
+    }
+
+  if (scoped) {
+    // ---- kernel, scope-local staging: per tile, every chunk stages its own features from the feature-major
+    // copy (thread = sample: coalesced global reads, conflict-free shared writes, no transposition) --------
+    // CF: per chunk its value features, then (feature, lo, domain) per code feature
+    std::vector<size_t> cfOff(nChunks);
+    o << "__device__ const int CF[] = {";
+    size_t cfN = 0;
+    for (size_t c = 0; c < nChunks; ++c) {
+      cfOff[c] = cfN;
+      for (int32_t f : chunkValueFeat[c]) { o << (cfN ? "," : "") << f; ++cfN; }
+      for (int32_t f : chunkCodeFeat[c]) { o << (cfN ? "," : "") << f << "," << p.features[f].lo << "," << p.features[f].domain; cfN += 3; }
+    }
+    if (!cfN) o << "0";
+    o << "};\n";
+    // One staging routine for all chunks, out of line: the kernel below stays a short list of calls (the
+    // JIT's time grows quadratically with the memory operations it sees in one function).
+    o << "typedef " << (cb == 1 ? "unsigned char" : "unsigned short") << " code_t;\n";
+    o << "static __device__ __noinline__ int spnb_stage(unsigned char* __restrict__ smem, const float* __restrict__ src, const unsigned long long ld,\n"
+         "                                              const int* __restrict__ cf, const int nv, const int nc, const unsigned codeBase, const unsigned tid)\n{\n";
+    o << "  float* xs = reinterpret_cast<float*>(smem);\n  code_t* cs = reinterpret_cast<code_t*>(smem + codeBase);\n  int nan = 0;\n";
+    o << "#pragma unroll 8\n";
+    o << "  for (int j = 0; j < nv; ++j) { const float raw = src[(unsigned long long)__ldg(cf + j) * ld]; xs[j * SX + tid] = raw; nan |= (raw != raw); }\n";
+    o << "  cf += nv;\n";
+    o << "#pragma unroll 8\n";
+    o << "  for (int j = 0; j < nc; ++j) {\n";
+    o << "    const float raw = src[(unsigned long long)__ldg(cf + 3 * j) * ld];\n";
+    o << "    const unsigned rr = (unsigned)TOINT(raw) - (unsigned)__ldg(cf + 3 * j + 1);\n";
+    o << "    int code = rr < (unsigned)__ldg(cf + 3 * j + 2) ? (int)rr + 2 : 1;\n";
+    o << "    if (raw != raw) code = 0;\n";
+    o << "    cs[j * SX + tid] = (code_t)code;\n";
+    o << "  }\n  return nan;\n}\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(TILE, 1)\n";
+    o << "spnb_kernel(const float* __restrict__ xt, out_t* __restrict__ out, unsigned long long n, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, real_t* __restrict__ scratch, unsigned long long ld)\n{\n";
+    if (nCross > 0) o << "  real_t* sc = scratch + ((size_t)blockIdx.x * " << (size_t)nCross << "u * TILE + threadIdx.x);\n";
+    else o << "  real_t* sc = scratch;\n";
+    o << "  extern __shared__ __align__(16) unsigned char smem_raw[];\n";
+    o << "  const unsigned tid = threadIdx.x;\n";
+    o << "  const unsigned xs_s = (unsigned)__cvta_generic_to_shared(smem_raw);\n";
+    o << "  unsigned tab_s = 0, lut_s = 0;\n";
+    o << "  uint4* win = reinterpret_cast<uint4*>(smem_raw + " << offTab << ");\n";
+    if (tabSmem) {
+      o << "  tab_s = (unsigned)__cvta_generic_to_shared(win);\n";
+      if (!streamed) o << "  for (unsigned i = tid; i < NTAB; i += TILE) reinterpret_cast<real_t*>(win)[i] = tab_g[i];\n";
+    }
+    if (lutSmem) {
+      o << "  { unsigned char* lut = smem_raw + " << offLut << ";\n";
+      o << "    for (unsigned i = tid; i < NLUT; i += TILE) lut[i] = lut_g[i];\n    lut_s = (unsigned)__cvta_generic_to_shared(lut); }\n";
+    }
+    o << "  const unsigned long long ntiles = (n + TILE - 1) / TILE;\n";
+    o << "#pragma unroll 1\n";
+    o << "  for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+    o << "    const unsigned long long base = tile * TILE;\n";
+    o << "    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
+    o << "    // threads past the end of the batch repeat its last sample; their result is not stored\n";
+    o << "    const float* __restrict__ src = xt + base + (tid < rows ? tid : rows - 1);\n";
+    o << "    out_t res = (out_t)0;\n";
+    for (size_t c = 0; c < nChunks; ++c) {
+      const size_t nv = chunkValueFeat[c].size(), nc = chunkCodeFeat[c].size();
+      o << "    {  // chunk " << c << ": " << nv << " staged values, " << nc << " staged codes\n";
+      o << "      __syncthreads();\n";
+      const bool choose = twoBodies && nv > 0;
+      o << "      " << (choose ? "const int nan = " : "") << "spnb_stage(smem_raw, src, ld, CF + " << cfOff[c] << ", " << nv << ", " << nc << ", "
+        << codeBase(c) << "u, tid);\n";
+      const std::string args = "(xs_s, xs_s + " + std::to_string(codeBase(c)) + "u, tab_s, lut_s, tab_g, lut_g, win, sc, tid);\n";
+      const std::string lhs = c + 1 == nChunks ? "res = " : "";
+      if (choose) {
+        o << "      if (__syncthreads_or(nan)) " << lhs << "spnb_body_nan" << c << args;
+        o << "      else " << lhs << "spnb_body" << c << args;
+      } else {
+        o << "      __syncthreads();\n";
+        o << "      " << lhs << "spnb_body" << c << args;
+      }
+      o << "    }\n";
+    }
+    o << "    if (tid < rows) out[base + tid] = res;\n";
+    o << "  }\n}\n";
+    if (info) {
+      info->kernelName = "spnb_kernel";
+      info->tile = TILE;
+      info->inputStride = SX;
+      info->tablesInSmem = tabSmem;
+      info->tableEntries = tabEntries;
+      info->dynamicSmemBytes = smemTotal;
+      info->scratchSlots = nCross;
+      info->scoped = true;
+      info->numChunks = (int)nChunks;
+    }
+    return o.str();
+  }
+
+  if (asyncStage) {
+    // ---- kernel, asynchronous staging: the next tile travels into the other buffer while this one is
+    // evaluated; rows are stored in order with stride RS words ---------------------------------------------
+    o << "#define RS " << RS << "\n";
+    o << "extern \"C\" __global__ void __launch_bounds__(TILE, " << minBlocks << ")\n";
+    o << "spnb_kernel(const in_t* __restrict__ in, out_t* __restrict__ out, unsigned long long n, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, real_t* __restrict__ scratch)\n{\n";
+    if (nCross > 0) o << "  real_t* sc = scratch + ((size_t)blockIdx.x * " << (size_t)nCross << "u * TILE + threadIdx.x);\n";
+    else o << "  real_t* sc = scratch;\n";
+    o << "  extern __shared__ __align__(16) unsigned char smem_raw[];\n";
+    o << "  const unsigned tid = threadIdx.x;\n";
+    o << "  const unsigned buf_s = (unsigned)__cvta_generic_to_shared(smem_raw);\n";
+    o << "  uint4* win = reinterpret_cast<uint4*>(smem_raw + " << offTab << ");\n";
+    o << "  const unsigned long long ntiles = (n + TILE - 1) / TILE;\n";
+    o << "  // copy of one tile: element e of the tile's row-major block goes to word (e / NF) * RS + e % NF\n";
+    o << "  auto issue = [&](unsigned long long tile, unsigned buf) {\n";
+    o << "    const unsigned long long base = tile * TILE;\n";
+    o << "    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
+    o << "    const in_t* __restrict__ src = in + base * NF;\n";
+    o << "    const unsigned total = rows * NF;\n";
+    o << "    const unsigned dst = buf_s + buf * " << asyncBuf << "u;\n";
+    o << "#pragma unroll 4\n";
+    o << "    for (unsigned e = tid; e < total; e += TILE) {\n";
+    o << "      const unsigned r = e / NF;\n";
+    o << "      asm volatile(\"cp.async.ca.shared.global [%0], [%1], 4;\" :: \"r\"(dst + 4u * (e + r * (RS - NF))), \"l\"(src + e) : \"memory\");\n";
+    o << "    }\n";
+    o << "    asm volatile(\"cp.async.commit_group;\" ::: \"memory\");\n";
+    o << "  };\n";
+    o << "  if (blockIdx.x < ntiles) issue(blockIdx.x, 0u);\n";
+    o << "  unsigned cur = 0;\n";
+    o << "#pragma unroll 1\n";
+    o << "  for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
+    o << "    const unsigned long long base = tile * TILE;\n";
+    o << "    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
+    o << "    asm volatile(\"cp.async.wait_group 0;\" ::: \"memory\");\n";
+    o << "    __syncthreads();   // this tile has landed for every thread; the other buffer's readers are done\n";
+    o << "    if (tile + gridDim.x < ntiles) issue(tile + gridDim.x, cur ^ 1u);\n";
+    o << "    const unsigned xs_s = buf_s + cur * " << asyncBuf << "u;\n";
+    o << "    out_t res;\n";
+    auto chainA = [&](const char* prefix, const std::string& in2) {
+      for (size_t c = 0; c < nChunks; ++c)
+        o << in2 << (c + 1 == nChunks ? "res = " : "") << prefix << c << "(xs_s, 0u, 0u, 0u, tab_g, lut_g, win, sc, tid);\n";
+    };
+    if (twoBodies) {
+      o << "    int nan = 0;\n";
+      o << "    if (tid < rows) {\n      const float* row = reinterpret_cast<const float*>(smem_raw + cur * " << asyncBuf << "u) + tid * RS;\n";
+      o << "#pragma unroll\n      for (int c = 0; c < NF; ++c) nan |= (row[c] != row[c]);\n    }\n";
+      o << "    if (__syncthreads_or(nan)) {\n";
+      chainA("spnb_body_nan", "      ");
+      o << "    } else {\n";
+      chainA("spnb_body", "      ");
+      o << "    }\n";
+    } else {
+      chainA("spnb_body", "    ");
+    }
+    o << "    if (tid < rows) out[base + tid] = res;\n";
+    o << "    cur ^= 1u;\n";
+    o << "  }\n}\n";
+    if (info) {
+      info->kernelName = "spnb_kernel";
+      info->tile = TILE;
+      info->inputStride = RS;
+      info->tablesInSmem = tabSmem;
+      info->tableEntries = tabEntries;
+      info->dynamicSmemBytes = smemTotal;
+      info->scratchSlots = nCross;
+      info->scoped = false;
+      info->numChunks = (int)nChunks;
+    }
+    return o.str();
+  }
 
   // ---- kernel: persistent CTAs, stage a tile of TILE samples, evaluate, store -------------------
   o << "extern \"C\" __global__ void __launch_bounds__(TILE, " << minBlocks << ")\n";
@@ -535,6 +793,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     info->tableEntries = tabEntries;
     info->dynamicSmemBytes = smemTotal;
     info->scratchSlots = nCross * std::max(groupTiles, 1);
+    info->scoped = false;
+    info->numChunks = (int)nChunks;
   }
   return o.str();
 }

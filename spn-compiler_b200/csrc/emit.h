@@ -20,6 +20,19 @@ struct EmitOptions {
   bool bucketArith = false;  // histogram buckets by multiply-shift where that reproduces the byte table exactly
                              // (off: five ALU instructions per leaf cost more than the shared-memory read they save)
   int smemTableLimit = 64 * 1024;  // shared-memory window for leaf tables; larger tables are streamed through it
+  // Scope-local staging.  When the inputs of 1024 samples do not fit into shared memory at once (hundreds of
+  // features), the DAG is cut into chunks whose leaves read few enough features, and every chunk stages only
+  // its own features for the tile, from a feature-major float copy of the batch (made by a small kernel before
+  // the launch, coalesced to read).  The CTA keeps 1024 threads, so every fetched instruction of the huge
+  // straight-line body serves 32 warps.  -1 = automatic (float32 inputs, log space, more than one chunk, and a
+  // CTA of 1024 samples impossible otherwise), 0 = never, 1 = whenever the inputs are float32 in log space.
+  int scoped = -1;
+  int scopeBytes = 0;              // staged bytes per sample and chunk (0 = what fits beside the table window)
+  // Asynchronous double-buffered staging (float32 inputs that are all read as values, log space): tile t + 1 is
+  // copied global -> shared with cp.async while tile t is evaluated.  Rows keep their order with an odd stride,
+  // so neither the copy nor the body's reads conflict on shared-memory banks and nothing is transposed.
+  // Used when two such buffers fit for the CTA size the single-buffer layout would get.  0 = off.
+  int asyncStage = 1;
 };
 
 struct EmitInfo {
@@ -30,6 +43,8 @@ struct EmitInfo {
   bool tablesInSmem = false;
   size_t tableEntries = 0;
   int scratchSlots = 0;     // scratch values per CTA thread: cross-chunk values x tiles per group
+  bool scoped = false;      // kernel reads a feature-major float copy:  (xt, out, n, tab, lut, scratch, ld)
+  int numChunks = 1;
 };
 
 std::string emitCuda(const Plan& plan, const EmitOptions& opt, EmitInfo* info);

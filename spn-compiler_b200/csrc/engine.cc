@@ -123,7 +123,7 @@ int dtypeCode(const FeatureType& t) {
 }
 
 // ---- plan file -----------------------------------------------------------------------------------
-const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '3'};
+const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '4'};
 
 struct Writer {
   std::vector<uint8_t> b;
@@ -153,7 +153,7 @@ std::string makeStatsJson(const Plan& p, Strategy s, const EmitInfo& ei, int reg
   o << base << ",\"log_space\":" << (p.logSpace ? "true" : "false") << ",\"strategy\":\""
     << (s == kUnrolled ? "unrolled" : (s == kInterpreter ? "interpreter" : "layered")) << "\",\"tile\":" << ei.tile << ",\"registers\":" << regs
     << ",\"spill_bytes\":" << spill << ",\"smem_bytes\":" << ei.dynamicSmemBytes << ",\"interp_slots\":" << interpSlots
-    << ",\"scratch_slots\":" << ei.scratchSlots << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
+    << ",\"scratch_slots\":" << ei.scratchSlots << ",\"chunks\":" << ei.numChunks << ",\"scoped_staging\":" << (ei.scoped ? "true" : "false") << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
   return o.str();
 }
 
@@ -222,6 +222,9 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
       o.tcWarpgroups = std::atoi(v.c_str());
       if (o.tcWarpgroups != 1 && o.tcWarpgroups != 2 && o.tcWarpgroups != 4) fail("spnb-tc-warpgroups must be 1, 2 or 4");
     }
+    else if (k == "spnb-scoped") o.scoped = std::atoi(v.c_str());
+    else if (k == "spnb-async-stage") o.asyncStage = std::atoi(v.c_str());
+    else if (k == "spnb-scope-bytes") o.scopeBytes = std::atoi(v.c_str());
     else if (k == "spnb-tc-tiles") {
       o.tcTiles = std::atoi(v.c_str());
       if (o.tcTiles != 1 && o.tcTiles != 2) fail("spnb-tc-tiles must be 1 or 2");
@@ -259,12 +262,11 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     int64_t maxFanIn = 0;
     for (size_t v = 0; v < plan.dag.size(); ++v)
       if (plan.dag.kind[v] == kSum) maxFanIn = std::max<int64_t>(maxFanIn, plan.dag.childPtr[v + 1] - plan.dag.childPtr[v]);
-    strat = (size <= opt.unrollLimit && (maxFanIn <= 64 || !opt.logSpace)) ? kUnrolled : kInterpreter;
+    // (linear space: sums up to 256 addends still unroll quickly, they are plain multiply-add chains)
+    strat = (size <= opt.unrollLimit && maxFanIn <= (opt.logSpace ? 64 : 256)) ? kUnrolled : kInterpreter;
     // dense layered models too large to unroll get the layered kernel instead of the interpreter
     if (strat == kInterpreter && opt.logSpace && recogniseLayers(plan.dag, &layered)) strat = kLayered;
   }
-  if (strat == kInterpreter && !opt.logSpace)
-    fail("The interpreter kernel evaluates in log space only; pass use-log-space=true for a DAG of this size");
 
   EmitInfo ei;
   std::string source;
@@ -285,6 +287,9 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
     eo.useMax3 = jitVersion() >= 1209;
     eo.bucketArith = opt.bucketArith != 0;
+    eo.scoped = opt.scoped;
+    eo.asyncStage = opt.asyncStage;
+    eo.scopeBytes = opt.scopeBytes;
     source = emitCuda(plan, eo, &ei);
     if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
     jr = jitCompile(source, m.name, opt.optLevel, opt.maxRegisters);
@@ -324,6 +329,8 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   w.u64((uint64_t)ei.tile);
   w.u64((uint64_t)ei.dynamicSmemBytes);
   w.u64((uint64_t)ei.scratchSlots);
+  w.u64((uint64_t)(ei.scoped ? 1 : 0));
+  w.u64((uint64_t)ei.numChunks);
   w.u64((uint64_t)(jr.registers + 1));
   w.u64((uint64_t)(jr.spillBytes + 1));
   w.blob(xspn.data(), xspn.size());
@@ -353,6 +360,7 @@ struct Engine::DeviceState {
   CUfunction fn = nullptr;
   void* dTab = nullptr;
   void* dLut = nullptr;
+  void* dConsts = nullptr;
   int* dProg = nullptr;
   int* dBreaks = nullptr;
   int4* dMeta = nullptr;
@@ -378,7 +386,8 @@ struct Engine::DeviceState {
   void* dDualCols = nullptr;
   void* dDualCentres = nullptr;
   int samplesPerCta = 0;     // samples one CTA takes per step of its tile loop, if not the block size
-  size_t layeredChunkRows = 0;
+  size_t layeredChunkRows = 0;   // samples copied feature-major at a time (layered kernels, scoped generated kernels)
+  size_t crossBytes = 0;         // scoped generated kernels: bytes of cross-chunk scratch in front of that copy
   int* dStatus = nullptr;
   // per-CTA scratch of a chunked generated kernel, [grid][slots][tile] values; one area per stream,
   // because launches on different streams may overlap on the GPU
@@ -407,6 +416,7 @@ struct Engine::DeviceState {
     if (hOut) cudaFreeHost(hOut);
     if (dTab) cudaFree(dTab);
     if (dLut) cudaFree(dLut);
+    if (dConsts) cudaFree(dConsts);
     if (dProg) cudaFree(dProg);
     if (dBreaks) cudaFree(dBreaks);
     if (dMeta) cudaFree(dMeta);
@@ -447,6 +457,8 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->emitInfo_.tile = (int)r.u64();
   e->emitInfo_.dynamicSmemBytes = (size_t)r.u64();
   e->emitInfo_.scratchSlots = (int)r.u64();
+  e->emitInfo_.scoped = r.u64() != 0;
+  e->emitInfo_.numChunks = (int)r.u64();
   int regs = (int)r.u64() - 1;
   int spill = (int)r.u64() - 1;
   std::vector<uint8_t> xspn = r.blob();
@@ -543,6 +555,13 @@ Engine::DeviceState& Engine::state(int device) {
     st->grid = perSM * st->smCount;
     if (emitInfo_.scratchSlots > 0) {
       st->scratchBytes = (size_t)st->grid * emitInfo_.scratchSlots * st->block * (p.logSpace ? 4 : 8);
+      st->scratchBytes = (st->scratchBytes + 255) & ~size_t(255);
+    }
+    if (emitInfo_.scoped) {
+      // the feature-major float copy of (a part of) the batch lives behind the cross-chunk values
+      st->crossBytes = st->scratchBytes;
+      st->layeredChunkRows = 512 * 1024;
+      st->scratchBytes += st->layeredChunkRows * (size_t)p.features.size() * 4;
     }
   } else if (strategy_ == kLayered) {
     LayeredPlan lp;
@@ -824,7 +843,9 @@ Engine::DeviceState& Engine::state(int device) {
       meta[f] = make_int4(p.features[f].lo, p.features[f].domain, p.features[f].codeSlot, p.features[f].valueSlot);
     st->dBreaks = (int*)upload(p.groupBreaks.data(), p.groupBreaks.size() * 4);
     st->dMeta = (int4*)upload(meta.data(), meta.size() * sizeof(int4));
-    st->ia.tab = (const float*)st->dTab;
+    st->ia.tab = st->dTab;
+    st->ia.linear = p.logSpace ? 0 : 1;
+    const size_t valueBytes = p.logSpace ? 4 : 8;
     st->ia.lut = (const unsigned char*)st->dLut;
     st->ia.breaks = st->dBreaks;
     st->ia.featureMeta = st->dMeta;
@@ -843,7 +864,7 @@ Engine::DeviceState& Engine::state(int device) {
       st->ia.numSlots = 0;
       const size_t base = interpSmemBytes(st->ia, t);
       if (base >= budget) continue;
-      int fit = (int)std::min<size_t>((budget - base) / ((size_t)t * 4), (size_t)need);
+      int fit = (int)std::min<size_t>((budget - base) / ((size_t)t * valueBytes), (size_t)need);
       if (interpSlotsCap_ > 0) fit = std::min(fit, interpSlotsCap_);
       if (fit >= std::min(need, interpSlotsCap_ > 0 ? interpSlotsCap_ : 48)) { tile = t; smemSlots = fit; break; }
     }
@@ -855,15 +876,17 @@ Engine::DeviceState& Engine::state(int device) {
     st->ia.numSlots = smemSlots;
     st->ia.numSpillSlots = plan_.numSpillSlots;
     st->dProg = (int*)upload(plan_.prog.data(), plan_.prog.size() * 4);
+    st->dConsts = upload(plan_.progConsts.data(), plan_.progConsts.size() * 8);
+    st->ia.dconst = (const double*)st->dConsts;
     st->ia.prog = st->dProg;
     st->ia.progLen = (int)plan_.prog.size();
     st->block = tile;
     st->smem = interpSmemBytes(st->ia, tile);
     int perSM = 0;
-    CUDA_OK(interpOccupancy(dtypeCode(p.ftype), tile, st->smem, &perSM));
+    CUDA_OK(interpOccupancy(dtypeCode(p.ftype), tile, st->smem, &perSM, !p.logSpace));
     if (perSM < 1) fail("Interpreter kernel does not fit on one SM");
     st->grid = perSM * st->smCount;
-    st->scratchBytes = (size_t)st->grid * plan_.numSpillSlots * st->block * 4;
+    st->scratchBytes = (size_t)st->grid * plan_.numSpillSlots * st->block * valueBytes;
   }
   auto ins = dev_.emplace(device, std::move(st));
   return *ins.first->second;
@@ -913,10 +936,28 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
   const size_t tiles = (n + (size_t)st.block - 1) / (size_t)st.block;
   const int grid = (int)std::min<size_t>(tiles, (size_t)st.grid);
   if (strategy_ == kUnrolled) {
-    unsigned long long nn = n;
     void* dScratch = scratchFor(st, stream);
-    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch};
     Driver& drv = Driver::get();
+    if (emitInfo_.scoped) {
+      // feature-major float copy first (at most layeredChunkRows samples at a time), then the kernel on it
+      float* xt = reinterpret_cast<float*>(static_cast<char*>(dScratch) + st.crossBytes);
+      const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature, resBytes = meta_.bytesPerResult;
+      for (size_t r0 = 0; r0 < n; r0 += st.layeredChunkRows) {
+        const size_t rows = std::min(st.layeredChunkRows, n - r0);
+        unsigned long long ld = (rows + 255) / 256 * 256, nn = rows;
+        const void* src = (const char*)dIn + r0 * rowBytes;
+        void* dst = (char*)dOut + r0 * resBytes;
+        CUDA_OK(transposeInputs(dtypeCode(plan_.ftype), src, xt, rows, (int)meta_.numFeatures, ld, stream));
+        const size_t tilesC = (rows + (size_t)st.block - 1) / (size_t)st.block;
+        const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);
+        void* args[] = {(void*)&xt, (void*)&dst, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch, (void*)&ld};
+        drv.check(drv.launchKernel(st.fn, gridC, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
+                  "cuLaunchKernel");
+      }
+      return;
+    }
+    unsigned long long nn = n;
+    void* args[] = {(void*)&dIn, (void*)&dOut, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch};
     drv.check(drv.launchKernel(st.fn, grid, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
   } else if (strategy_ == kLayered) {
@@ -946,8 +987,8 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     }
   } else {
     InterpArgs ia = st.ia;
-    ia.scratch = (float*)scratchFor(st, stream);
-    CUDA_OK(interpLaunch(ia, dtypeCode(plan_.ftype), dIn, (float*)dOut, n, grid, st.block, st.smem, stream));
+    ia.scratch = scratchFor(st, stream);
+    CUDA_OK(interpLaunch(ia, dtypeCode(plan_.ftype), dIn, dOut, n, grid, st.block, st.smem, stream));
   }
 }
 

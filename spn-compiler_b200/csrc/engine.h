@@ -41,6 +41,9 @@ struct Options {
   int chunkNodes = -1;         // "spnb-chunk-nodes": DAG nodes per generated function (-1 = default, 0 = one function)
   int mmaSplit = 1;            // "spnb-mma-split": 1 = half-precision operands carry their rounding residue (3 MMAs), 0 = plain fp16
   int tcWarpgroups = 1;        // "spnb-tc-warpgroups": warpgroups (128 threads) per CTA of the tensor-memory layered kernel
+  int scoped = -1;             // "spnb-scoped": scope-local staging of a chunked generated kernel (-1 automatic, 0 off, 1 on)
+  int asyncStage = 1;          // "spnb-async-stage": 0 = never stage the next tile with cp.async while one is evaluated
+  int scopeBytes = 0;          // "spnb-scope-bytes": staged bytes per sample and chunk (0 = what fits)
   int tcTiles = 2;             // "spnb-tc-tiles": 2 = two sample tiles per CTA where the model allows it, 1 = one tile
   long long spinLimit = 0;     // "spnb-spin-limit": polls after which a tensor-core barrier wait gives up (0 = 2^22)
   int selftestWithhold = 0;    // "spnb-selftest-withhold-commit": 1 = the two-tile kernel leaves out one commit (tests

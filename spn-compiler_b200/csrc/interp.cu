@@ -12,6 +12,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "interp.h"
 
@@ -49,25 +50,32 @@ template <typename T> struct IsFloat { static constexpr bool value = false; };
 template <> struct IsFloat<float> { static constexpr bool value = true; };
 template <> struct IsFloat<double> { static constexpr bool value = true; };
 
-// Shared memory: [fm int4 x F][xs float x NV*SX][cs u16 x NC*SX][pad to 4][vals float x nslots*TILE]
-template <typename in_t>
-__global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* __restrict__ in, float* __restrict__ out,
+// Shared memory: [fm int4 x F][xs real x NV*SX][cs u16 x NC*SX][pad to 8][vals real x nslots*TILE]
+// LINEAR = false: values are base-2 logarithms in float (products add, sums are max-shifted log-sum-exp).
+// LINEAR = true:  values are probabilities in double, one natural log at the root: the reference's f64 mode
+// (mlir/lib/Conversion/HiSPNtoLoSPN/NodePatterns.cpp:140-151) for DAGs too large or too wide to unroll; the
+// op stream then names its constants (Gaussian parameters, sum weights) by index into a table of doubles.
+template <typename in_t, bool LINEAR>
+__global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* __restrict__ in, void* __restrict__ outv,
                                                        unsigned long long n) {
+  using real = typename std::conditional<LINEAR, double, float>::type;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const unsigned tid = threadIdx.x;
   const unsigned TILE = blockDim.x;
   const unsigned SX = TILE + 1;
   const unsigned F = a.numFeatures;
   int4* fm = reinterpret_cast<int4*>(smem_raw);
-  float* xs = reinterpret_cast<float*>(smem_raw + (size_t)F * 16);
+  real* xs = reinterpret_cast<real*>(smem_raw + (size_t)F * 16);
   unsigned short* cs = reinterpret_cast<unsigned short*>(xs + (size_t)a.numValueSlots * SX);
-  float* vals = reinterpret_cast<float*>(smem_raw + a.valsOffset(TILE));
+  real* vals = reinterpret_cast<real*>(smem_raw + a.valsOffset(TILE));
   for (unsigned i = tid; i < F; i += TILE) fm[i] = a.featureMeta[i];
   const int* __restrict__ prog = a.prog;
-  const float* __restrict__ tab = a.tab;
+  const real* __restrict__ tab = static_cast<const real*>(a.tab);
+  const double* __restrict__ dc = a.dconst;
   const unsigned char* __restrict__ lut = a.lut;
   const int* __restrict__ brk = a.breaks;
   const bool marginal = a.marginal != 0;
+  real* out = static_cast<real*>(outv);
 
   const unsigned long long ntiles = (n + TILE - 1) / TILE;
   for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
@@ -78,47 +86,57 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
       const in_t* __restrict__ src = in + base * F;
       const unsigned total = rows * F;
       unsigned r = tid / F, c = tid - r * F;          // element e = tid + i*TILE -> (row, column)
-      const unsigned dr = TILE / F, dc = TILE - dr * F;
+      const unsigned dr = TILE / F, dcol = TILE - dr * F;
       for (unsigned e = tid; e < TILE * F; e += TILE) {
         const int4 m = fm[c];
         const bool live = e < total;
         in_t raw = 0;
         if (live) raw = src[e];
-        if (m.w >= 0) xs[m.w * SX + r] = (float)raw;
+        if (m.w >= 0) xs[m.w * SX + r] = (real)raw;
         if (m.z >= 0) {
           const unsigned rr = (unsigned)toIntSat<in_t>(raw) - (unsigned)m.x;
           int code = rr < (unsigned)m.y ? (int)rr + 2 : 1;
           if (IsFloat<in_t>::value && raw != raw) code = 0;
           cs[m.z * SX + r] = (unsigned short)(live ? code : 1);
         }
-        r += dr; c += dc;
+        r += dr; c += dcol;
         if (c >= F) { c -= F; r += 1; }
       }
     }
     __syncthreads();
-    const float* xcol = xs + tid;
+    const real* xcol = xs + tid;
     const unsigned short* ccol = cs + tid;
-    float* v = vals + tid;
+    real* v = vals + tid;
     // value slots: ids below numSlots are shared memory, the rest this CTA's part of the scratch area
     const int S = a.numSlots;
-    float* g = a.scratch + ((size_t)blockIdx.x * a.numSpillSlots * TILE + tid);
-    auto ld = [&](int s) -> float { return s < S ? v[s * TILE] : g[(size_t)(s - S) * TILE]; };
+    real* g = static_cast<real*>(a.scratch) + ((size_t)blockIdx.x * a.numSpillSlots * TILE + tid);
+    auto ld = [&](int s) -> real { return s < S ? v[s * TILE] : g[(size_t)(s - S) * TILE]; };
     int pc = 0;
     // the walk is bounded by the program length: a corrupt stream ends the tile instead of spinning
     while (pc < a.progLen) {
       const int op = __ldg(prog + pc);
       if (op == OP_END) {
-        if (tid < rows) out[base + tid] = ld(__ldg(prog + pc + 1)) * 0x1.62e43p-1f;
+        const real root = ld(__ldg(prog + pc + 1));
+        if (tid < rows) {
+          if (LINEAR) out[base + tid] = (real)log((double)root);
+          else out[base + tid] = root * (real)0x1.62e43p-1f;
+        }
         break;
       }
       const int dst = __ldg(prog + pc + 1);
-      float r;
+      real r;
       switch (op) {
         case OP_GAUSS: {
-          const float x = xcol[__ldg(prog + pc + 2) * SX];
-          const float d = x - __int_as_float(__ldg(prog + pc + 3));
-          r = fmaf(d * d, __int_as_float(__ldg(prog + pc + 4)), __int_as_float(__ldg(prog + pc + 5)));
-          if (marginal && d != d) r = 0.0f;
+          const real x = xcol[__ldg(prog + pc + 2) * SX];
+          if (LINEAR) {
+            const double d = (double)x - __ldg(dc + __ldg(prog + pc + 3));
+            r = (real)(__ldg(dc + __ldg(prog + pc + 5)) * exp((d * d) * __ldg(dc + __ldg(prog + pc + 4))));
+            if (marginal && d != d) r = (real)1;
+          } else {
+            const float d = (float)x - __int_as_float(__ldg(prog + pc + 3));
+            r = (real)fmaf(d * d, __int_as_float(__ldg(prog + pc + 4)), __int_as_float(__ldg(prog + pc + 5)));
+            if (marginal && d != d) r = (real)0;
+          }
           pc += 6;
           break;
         }
@@ -131,10 +149,10 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
           break;
         }
         case OP_HISTG: {
-          const float x = xcol[__ldg(prog + pc + 2) * SX];
+          const real x = xcol[__ldg(prog + pc + 2) * SX];
           const int* b = brk + __ldg(prog + pc + 3);
           const int cnt = __ldg(prog + pc + 4);
-          const int xi = __float2int_rz(x);
+          const int xi = LINEAR ? __double2int_rz((double)x) : __float2int_rz((float)x);
           int idx = cnt;
           if (xi >= __ldg(b) && xi < __ldg(b + cnt)) {
             idx = 0;
@@ -148,31 +166,53 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
         case OP_PROD: {
           const int k = min(__ldg(prog + pc + 2), a.progLen - pc);
           const int* s = prog + pc + 3;
-          float a0 = 0.0f, a1 = 0.0f;
-          int i = 0;
-          for (; i + 1 < k; i += 2) {
-            a0 += ld(__ldg(s + i));
-            a1 += ld(__ldg(s + i + 1));
+          if (LINEAR) {
+            real a0 = (real)1, a1 = (real)1;
+            int i = 0;
+            for (; i + 1 < k; i += 2) {
+              a0 *= ld(__ldg(s + i));
+              a1 *= ld(__ldg(s + i + 1));
+            }
+            if (i < k) a0 *= ld(__ldg(s + i));
+            r = a0 * a1;
+          } else {
+            real a0 = (real)0, a1 = (real)0;
+            int i = 0;
+            for (; i + 1 < k; i += 2) {
+              a0 += ld(__ldg(s + i));
+              a1 += ld(__ldg(s + i + 1));
+            }
+            if (i < k) a0 += ld(__ldg(s + i));
+            r = a0 + a1;
           }
-          if (i < k) a0 += ld(__ldg(s + i));
-          r = a0 + a1;
           pc += 3 + k;
           break;
         }
         case OP_SUM: {
           const int k = min(__ldg(prog + pc + 2), (a.progLen - pc) / 2);
           const int* s = prog + pc + 3;
-          float m = __int_as_float(0xff800000);
-          for (int i = 0; i < k; ++i) m = fmaxf(m, ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)));
-          const float mm = (m == __int_as_float(0xff800000)) ? 0.0f : m;
-          float acc0 = 0.0f, acc1 = 0.0f;
-          int i = 0;
-          for (; i + 1 < k; i += 2) {
-            acc0 += ex2(ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
-            acc1 += ex2(ld(__ldg(s + 2 * i + 2)) + __int_as_float(__ldg(s + 2 * i + 3)) - mm);
+          if (LINEAR) {
+            double acc0 = 0.0, acc1 = 0.0;
+            int i = 0;
+            for (; i + 1 < k; i += 2) {
+              acc0 = fma(__ldg(dc + __ldg(s + 2 * i + 1)), (double)ld(__ldg(s + 2 * i)), acc0);
+              acc1 = fma(__ldg(dc + __ldg(s + 2 * i + 3)), (double)ld(__ldg(s + 2 * i + 2)), acc1);
+            }
+            if (i < k) acc0 = fma(__ldg(dc + __ldg(s + 2 * i + 1)), (double)ld(__ldg(s + 2 * i)), acc0);
+            r = (real)(acc0 + acc1);
+          } else {
+            float m = __int_as_float(0xff800000);
+            for (int i = 0; i < k; ++i) m = fmaxf(m, (float)ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)));
+            const float mm = (m == __int_as_float(0xff800000)) ? 0.0f : m;
+            float acc0 = 0.0f, acc1 = 0.0f;
+            int i = 0;
+            for (; i + 1 < k; i += 2) {
+              acc0 += ex2((float)ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
+              acc1 += ex2((float)ld(__ldg(s + 2 * i + 2)) + __int_as_float(__ldg(s + 2 * i + 3)) - mm);
+            }
+            if (i < k) acc0 += ex2((float)ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
+            r = (real)(m + lg2(acc0 + acc1));
           }
-          if (i < k) acc0 += ex2(ld(__ldg(s + 2 * i)) + __int_as_float(__ldg(s + 2 * i + 1)) - mm);
-          r = m + lg2(acc0 + acc1);
           pc += 3 + 2 * k;
           break;
         }
@@ -187,29 +227,40 @@ __global__ void __launch_bounds__(1024) interpKernel(InterpArgs a, const in_t* _
 }
 
 template <typename in_t>
-cudaError_t launchT(const InterpArgs& a, const void* in, float* out, size_t n, int grid, int tile, size_t smem,
+cudaError_t launchT(const InterpArgs& a, const void* in, void* out, size_t n, int grid, int tile, size_t smem,
                     cudaStream_t stream) {
-  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<in_t>), smem);
+  if (a.linear) {
+    cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<in_t, true>), smem);
+    if (e != cudaSuccess) return e;
+    interpKernel<in_t, true><<<grid, tile, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n);
+    return cudaGetLastError();
+  }
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<in_t, false>), smem);
   if (e != cudaSuccess) return e;
-  interpKernel<in_t><<<grid, tile, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n);
+  interpKernel<in_t, false><<<grid, tile, smem, stream>>>(a, static_cast<const in_t*>(in), out, (unsigned long long)n);
   return cudaGetLastError();
 }
 
 }  // namespace
 
 size_t interpSmemBytes(const InterpArgs& a, int tile) {
-  return a.valsOffset((unsigned)tile) + (size_t)a.numSlots * tile * 4;
+  return a.valsOffset((unsigned)tile) + (size_t)a.numSlots * tile * (a.linear ? 8 : 4);
 }
 
-cudaError_t interpOccupancy(int inKindCode, int tile, size_t smem, int* blocksPerSM) {
-  // all instantiations have the same resource usage up to the staging conversion; query the float one
+cudaError_t interpOccupancy(int inKindCode, int tile, size_t smem, int* blocksPerSM, bool linear) {
+  // all instantiations have the same resource usage up to the staging conversion; query the float-input ones
   (void)inKindCode;
-  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<float>), smem);
+  if (linear) {
+    cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<float, true>), smem);
+    if (e != cudaSuccess) return e;
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, interpKernel<float, true>, tile, smem);
+  }
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(&interpKernel<float, false>), smem);
   if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, interpKernel<float>, tile, smem);
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocksPerSM, interpKernel<float, false>, tile, smem);
 }
 
-cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
+cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, void* out, size_t n, int grid, int tile,
                          size_t smem, cudaStream_t stream) {
   switch (dtypeCode) {
     case DT_U8: return launchT<uint8_t>(a, in, out, n, grid, tile, smem, stream);
@@ -308,14 +359,14 @@ cudaError_t interpLaunchStatic(const InterpImage& img, InterpArgs a, int dtypeCo
     st.resident = img.tag;
   }
   a.prog = reinterpret_cast<const int*>(st.base + offProg);
-  a.tab = reinterpret_cast<const float*>(st.base + offTab);
+  a.tab = st.base + offTab;
   a.lut = st.base + offLut;
   a.breaks = reinterpret_cast<const int*>(st.base + offBrk);
   a.featureMeta = reinterpret_cast<const int4*>(st.base + offMeta);
   a.scratch = reinterpret_cast<float*>(st.base + offScratch);
   const size_t smem = interpSmemBytes(a, tile);
   int perSM = 0, sms = 0;
-  cudaError_t e = interpOccupancy(dtypeCode, tile, smem, &perSM);
+  cudaError_t e = interpOccupancy(dtypeCode, tile, smem, &perSM, false);
   if (e != cudaSuccess) return e;
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (e != cudaSuccess) return e;

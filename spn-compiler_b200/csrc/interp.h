@@ -17,7 +17,8 @@ enum DTypeCode : int { DT_U8 = 0, DT_I8, DT_U16, DT_I16, DT_U32, DT_I32, DT_U64,
 
 struct InterpArgs {
   const int* prog;              // device: op stream
-  const float* tab;             // device: leaf tables (log2 domain)
+  const void* tab;              // device: leaf tables (float, log2 domain; double probabilities in linear mode)
+  const double* dconst;         // device: linear mode: the constants the op stream refers to by index
   const unsigned char* lut;     // device: code -> bucket byte tables
   const int* breaks;            // device: breaks of the generic histogram groups
   const int4* featureMeta;      // device: per feature (lo, domain, codeSlot, valueSlot)
@@ -27,13 +28,15 @@ struct InterpArgs {
   int numCodeSlots;
   int numSlots;                 // value slots in shared memory
   int numSpillSlots;            // value slots in the scratch area
-  float* scratch;               // device: [grid][numSpillSlots][tile] floats, or null
+  void* scratch;                // device: [grid][numSpillSlots][tile] values, or null
   int marginal;
+  int linear;                   // 1: linear-space f64 evaluation with one log at the root (values are doubles)
   // byte offset of the value slots behind the staged inputs for a CTA of `tile` threads
   __host__ __device__ size_t valsOffset(unsigned tile) const {
     size_t sx = (size_t)tile + 1;
-    size_t o = (size_t)numFeatures * 16 + (size_t)numValueSlots * sx * 4 + (size_t)numCodeSlots * sx * 2;
-    return (o + 3) & ~(size_t)3;
+    size_t rb = linear ? 8 : 4;
+    size_t o = (size_t)numFeatures * 16 + (size_t)numValueSlots * sx * rb + (size_t)numCodeSlots * sx * 2;
+    return (o + 7) & ~(size_t)7;
   }
 };
 
@@ -55,8 +58,8 @@ inline cudaError_t ensureDynamicSmem(const void* kernel, size_t smem) {
 }
 
 size_t interpSmemBytes(const InterpArgs& a, int tile);
-cudaError_t interpOccupancy(int dtypeCode, int tile, size_t smem, int* blocksPerSM);
-cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
+cudaError_t interpOccupancy(int dtypeCode, int tile, size_t smem, int* blocksPerSM, bool linear);
+cudaError_t interpLaunch(const InterpArgs& a, int dtypeCode, const void* in, void* out, size_t n, int grid, int tile,
                          size_t smem, cudaStream_t stream);
 
 // ---- variant without device allocations ---------------------------------------------------------------

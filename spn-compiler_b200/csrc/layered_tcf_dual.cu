@@ -27,6 +27,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "interp.h"
 #include "layered.h"
 #include "layers.h"
@@ -135,6 +138,29 @@ __device__ __forceinline__ void tmemLoad32(unsigned taddr, unsigned* r) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same load without the wait: the registers are written some time before the matching tmemWait32, which
+// names them as in/out operands so that no use of them is scheduled ahead of it.
+__device__ __forceinline__ void tmemLoad32Async(unsigned taddr, unsigned* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmemWait32(unsigned* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void fenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fenceAsyncProxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -183,10 +209,25 @@ struct Waiter {
 
 // shared memory: [a-stack float x NTILE*aSlots*32*128][A operand 2 x 16 KB][weight ring ringBlocks x 16 KB]
 //                [leaf weight ring 4 x 2 KB][barriers][tmem address][abort flag]
-template <bool MARGINAL>
+// Development aid: with PROFILE the first CTA's tile-0 lane 0, issuer and loader accumulate the cycles they
+// spend per phase into prof[] (see layeredDualLaunch); the production instantiation carries none of it.
+enum ProfSlot {
+  P_W_TOTAL = 0, P_W_LEAF, P_W_LEAF_WAITEMPTY, P_W_LEAF_WAITDONE, P_W_INNER, P_W_INNER_PREP, P_W_INNER_WAITFULL,
+  P_W_INNER_FOLD, P_W_DELIVER, P_W_FOLD_LDWAIT, P_W_LEAF_BUILD, P_W_LEAF_ARRIVE,
+  P_I_TOTAL = 16, P_I_WAIT_WFULL, P_I_WAIT_OPREADY, P_I_WAIT_ACCFREE, P_I_WAIT_LWFULL, P_I_WAIT_LEAFFULL, P_I_LEAF, P_I_INNER, P_I_MMA, P_I_COMMIT, P_I_FENCE,
+  P_L_TOTAL = 32, P_L_WAIT_WEMPTY,
+  P_COUNT = 48
+};
+#define PROF_T() (PROFILE ? clock64() : 0ll)
+#define PROF_ADD(slot, t0) do { if (PROFILE && profOn) prof[slot] += clock64() - (t0); } while (0)
+
+template <bool MARGINAL, bool PROFILE>
 __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, const float* __restrict__ xt,
                                                                   float* __restrict__ out, unsigned long long n,
-                                                                  int* __restrict__ status) {
+                                                                  int* __restrict__ status, long long* __restrict__ profOut) {
+  long long prof[PROFILE ? P_COUNT : 1];
+  if (PROFILE) for (int i = 0; i < P_COUNT; ++i) prof[i] = 0;
+  const bool profOn = PROFILE && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x >= NWORK);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const unsigned tid = threadIdx.x;
   const unsigned warp = tid >> 5, lane = tid & 31;
@@ -242,6 +283,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
     unsigned phAccFull0 = 0, phAccFull1 = 0, phLeafEmpty0 = 0, phLeafEmpty1 = 0, phLeafDone = 0;
     unsigned pendEmpty0 = 0, pendEmpty1 = 0;
 
+    const long long tW = PROF_T();
     for (unsigned long long pair = blockIdx.x; pair < npairs && !failed; pair += gridDim.x) {
       const unsigned long long row = (pair * NTILE + t) * TS + r;
       const bool live = row < n;
@@ -318,6 +360,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
         const DualStepDev s = a.steps[si];
         float v[KMAX];
         if (s.op == kLeafRegion) {
+          const long long tL = PROF_T();
           const int nst = s.numBlocks;
           bool redo = nst == 0;     // regions without tensor-core weights are computed by the FP32 loop below
           if (nst > 0) {
@@ -331,10 +374,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
                   const int sb = d & 1;
                   // the MMAs that read this stage buffer two stages ago must be done
                   if (sb == 0 ? pendEmpty0 : pendEmpty1) {
+                    const long long tq = PROF_T();
                     if (!w.wait(bar(bT + BAR_LEAFEMPTY + sb), sb == 0 ? phLeafEmpty0 : phLeafEmpty1)) failed = true;
+                    PROF_ADD(P_W_LEAF_WAITEMPTY, tq);
                     if (sb == 0) { phLeafEmpty0 ^= 1; pendEmpty0 = 0; } else { phLeafEmpty1 ^= 1; pendEmpty1 = 0; }
                   }
                   if (!failed) {
+                    const long long tb = PROF_T();
                     unsigned char* adst = myA + sb * LEAF_STAGE + rowOff;
                     const float* cen = a.leafCentres + (size_t)(s.stageBase + st) * 4;
 #pragma unroll
@@ -356,9 +402,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
                       // feature 2 j of the stage is k 0..7 of k-step j, feature 2 j + 1 is k 8..15
                       *reinterpret_cast<uint4*>(adst + (u >> 1) * KSTEP_A + (u & 1) * (KSTEP_A / 2)) = q;
                     }
+                    PROF_ADD(P_W_LEAF_BUILD, tb);
+                    const long long ta = PROF_T();
                     fenceAsyncProxy();
                     __syncwarp();
                     if (lane == 0) mbarArrive(bar(bT + BAR_LEAFFULL + sb));
+                    PROF_ADD(P_W_LEAF_ARRIVE, ta);
                     if (sb == 0) pendEmpty0 = 1; else pendEmpty1 = 1;
                   }
                 }
@@ -367,7 +416,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
             }
             // accumulator complete; the stage barriers' last completions are consumed as well, so that every
             // phase of every barrier is waited for exactly once
+            const long long tq2 = PROF_T();
             if (!failed) { if (!w.wait(bar(BAR_LEAFDONE + t), phLeafDone)) failed = true; phLeafDone ^= 1; }
+            PROF_ADD(P_W_LEAF_WAITDONE, tq2);
             if (!failed && pendEmpty0) { if (!w.wait(bar(bT + BAR_LEAFEMPTY), phLeafEmpty0)) failed = true; phLeafEmpty0 ^= 1; pendEmpty0 = 0; }
             if (!failed && pendEmpty1) { if (!w.wait(bar(bT + BAR_LEAFEMPTY + 1), phLeafEmpty1)) failed = true; phLeafEmpty1 ^= 1; pendEmpty1 = 0; }
             if (failed) break;
@@ -404,10 +455,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
 #pragma unroll
           for (int k = 0; k < KMAX; ++k)
             if (k >= s.width) v[k] = NEG;
+          const long long tD = PROF_T();
           deliver(s, v);
+          PROF_ADD(P_W_DELIVER, tD);
+          PROF_ADD(P_W_LEAF, tL);
           continue;
         }
         // ---- inner region or root part -------------------------------------------------------------
+        const long long tI = PROF_T();
         if (s.aSrc >= 0) {
           const float* src = myStack + (size_t)s.aSrc * SLOT_FLOATS;
           ma = NEG;
@@ -430,6 +485,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
         const int nblk = s.numBlocks;
 #pragma unroll
         for (int k = 0; k < KMAX; ++k) v[k] = NEG;
+        PROF_ADD(P_W_INNER_PREP, tI);
 #pragma unroll
         for (int nb = 0; nb < KMAX * KMAX / NBLK; ++nb) {
           if (nb < nblk && !failed) {
@@ -437,26 +493,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
             float sc[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) sc[q] = __ldg(scale + 4 * nb + q);   // requested before the wait
+            const long long tq = PROF_T();
             if (!w.wait(bar(bT + BAR_ACCFULL + b), b == 0 ? phAccFull0 : phAccFull1)) failed = true;
+            PROF_ADD(P_W_INNER_WAITFULL, tq);
             if (b == 0) phAccFull0 ^= 1; else phAccFull1 ^= 1;
+            const long long tf = PROF_T();
             if (!failed) {
               fenceAfter();
+              // four sums per block; the accumulator columns of sum q + 1 travel from TMEM to registers while
+              // sum q is folded (two register buffers)
+              unsigned t0[KMAX], t1[KMAX];
+              const unsigned tcol = tmemAcc + b * NBLK;
+              const int nq = s.width - 4 * nb;   // sums of this block that exist (warp-uniform)
+              auto dot = [&](const unsigned* tt, int q) {
+                unsigned long long acc0 = 0ull, acc1 = 0ull, acc2 = 0ull, acc3 = 0ull;
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const int k = 4 * nb + q;
-                if (k < s.width) {
-                  unsigned tt[KMAX];
-                  tmemLoad32(tmemAcc + b * NBLK + q * KMAX, tt);
-                  unsigned long long acc0 = 0ull, acc1 = 0ull, acc2 = 0ull, acc3 = 0ull;
-#pragma unroll
-                  for (int i = 0; i < KMAX / 2; i += 4) {
-                    fma2(acc0, ea2[i], pack2u(tt[2 * i], tt[2 * i + 1]));
-                    fma2(acc1, ea2[i + 1], pack2u(tt[2 * i + 2], tt[2 * i + 3]));
-                    fma2(acc2, ea2[i + 2], pack2u(tt[2 * i + 4], tt[2 * i + 5]));
-                    fma2(acc3, ea2[i + 3], pack2u(tt[2 * i + 6], tt[2 * i + 7]));
-                  }
-                  v[k] = base + lg2f((sum2(acc0) + sum2(acc1)) + (sum2(acc2) + sum2(acc3))) + sc[q];
+                for (int i = 0; i < KMAX / 2; i += 4) {
+                  fma2(acc0, ea2[i], pack2u(tt[2 * i], tt[2 * i + 1]));
+                  fma2(acc1, ea2[i + 1], pack2u(tt[2 * i + 2], tt[2 * i + 3]));
+                  fma2(acc2, ea2[i + 2], pack2u(tt[2 * i + 4], tt[2 * i + 5]));
+                  fma2(acc3, ea2[i + 3], pack2u(tt[2 * i + 6], tt[2 * i + 7]));
                 }
+                v[4 * nb + q] = base + lg2f((sum2(acc0) + sum2(acc1)) + (sum2(acc2) + sum2(acc3))) + sc[q];
+              };
+              long long tw = PROF_T();
+              tmemLoad32Async(tcol, t0);
+              tmemWait32(t0);
+              PROF_ADD(P_W_FOLD_LDWAIT, tw);
+              if (nq > 1) tmemLoad32Async(tcol + KMAX, t1);
+              dot(t0, 0);
+              if (nq > 1) {
+                tw = PROF_T();
+                tmemWait32(t1);
+                PROF_ADD(P_W_FOLD_LDWAIT, tw);
+                if (nq > 2) tmemLoad32Async(tcol + 2 * KMAX, t0);
+                dot(t1, 1);
+              }
+              if (nq > 2) {
+                tw = PROF_T();
+                tmemWait32(t0);
+                PROF_ADD(P_W_FOLD_LDWAIT, tw);
+                if (nq > 3) tmemLoad32Async(tcol + 3 * KMAX, t1);
+                dot(t0, 2);
+              }
+              if (nq > 3) {
+                tw = PROF_T();
+                tmemWait32(t1);
+                PROF_ADD(P_W_FOLD_LDWAIT, tw);
+                dot(t1, 3);
               }
               // a later block's MMAs overwrite this accumulator: order the reads before the arrival that
               // allows them (the last two blocks are covered by the next region's operand arrival)
@@ -466,44 +550,62 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
                 if (lane == 0) mbarArrive(bar(bT + BAR_ACCFREE + b));
               }
             }
+            PROF_ADD(P_W_INNER_FOLD, tf);
           }
         }
         if (failed) break;
+        const long long tD = PROF_T();
         deliver(s, v);
+        PROF_ADD(P_W_DELIVER, tD);
+        PROF_ADD(P_W_INNER, tI);
       }
       if (live && !failed) out[row] = (rootM + lg2f(rootS)) * 0x1.62e43p-1f;
     }
+    PROF_ADD(P_W_TOTAL, tW);
   } else if (warp == 8) {
     // ================================ MMA issuer ====================================================
     const unsigned idescLeaf = (1u << 4) | ((unsigned)(KMAX >> 3) << 17) | ((unsigned)(TS >> 4) << 24);
     const unsigned idescSum = (1u << 4) | ((unsigned)(NBLK >> 3) << 17) | ((unsigned)(TS >> 4) << 24);
-    const unsigned aAddr = smemAddr(abuf), bAddr = smemAddr(bring), lwAddr = smemAddr(lwring);
-    unsigned phOpReady[NTILE] = {0, 0}, phAccFree[NTILE][2] = {{0, 0}, {0, 0}}, phLeafFull[NTILE][2] = {{0, 0}, {0, 0}};
+    // Descriptors of the operand areas' first blocks, built once: a block further on adds its byte offset / 16
+    // to the start-address field (the sum stays inside the field: shared memory ends below 256 KB).  Building a
+    // descriptor from scratch costs a dozen dependent integer instructions; with one thread issuing every MMA
+    // of the CTA that latency would sit in front of each of them.
+    const unsigned long long aDesc[NTILE] = {smemDesc(smemAddr(abuf), KSTEP_A / 2, 128),
+                                             smemDesc(smemAddr(abuf) + A_TILE, KSTEP_A / 2, 128)};
+    const unsigned long long bDesc0 = smemDesc(smemAddr(bring), KSTEP_B / 2, 128);
+    const unsigned long long lwDesc0 = smemDesc(smemAddr(lwring), KSTEP_BL / 2, 128);
+    unsigned phOpReady0 = 0, phOpReady1 = 0, phAccFree00 = 0, phAccFree01 = 0, phAccFree10 = 0, phAccFree11 = 0;
+    unsigned phLeafFull00 = 0, phLeafFull01 = 0, phLeafFull10 = 0, phLeafFull11 = 0;
     unsigned wCount = 0, lwCount = 0;   // blocks / leaf stages consumed so far: ring slot and parity
     bool withheld = a.testWithholdCommit == 0;
+    const long long tIs = PROF_T();
     for (unsigned long long pair = blockIdx.x; pair < npairs && !failed; pair += gridDim.x) {
       for (int si = 0; si < a.numSteps && !failed; ++si) {
         const DualStepDev s = a.steps[si];
+        const long long tStep = PROF_T();
         if (s.op == kLeafRegion) {
           const int nst = s.numBlocks;
 #pragma unroll 1
           for (int st = 0; st < nst && !failed; ++st) {
             const unsigned ring = lwCount % LW_RING;
+            const long long tq = PROF_T();
             if (!w.wait(bar(BAR_LWFULL + ring), (lwCount / LW_RING) & 1)) { failed = true; break; }
+            PROF_ADD(P_I_WAIT_LWFULL, tq);
             const int sb = st & 1;
+            const unsigned long long lwd = lwDesc0 + (unsigned)((ring * LW_STAGE) >> 4);
 #pragma unroll
             for (int t = 0; t < NTILE; ++t) {
               if (failed) break;
-              if (!w.wait(bar(t * BAR_TILE + BAR_LEAFFULL + sb), phLeafFull[t][sb])) { failed = true; break; }
-              phLeafFull[t][sb] ^= 1;
+              const long long tq3 = PROF_T();
+              unsigned& ph = t == 0 ? (sb == 0 ? phLeafFull00 : phLeafFull01) : (sb == 0 ? phLeafFull10 : phLeafFull11);
+              if (!w.wait(bar(t * BAR_TILE + BAR_LEAFFULL + sb), ph)) { failed = true; break; }
+              PROF_ADD(P_I_WAIT_LEAFFULL, tq3);
+              ph ^= 1;
               if (lane == 0) {
                 fenceAfter();
-#pragma unroll
-                for (int ks = 0; ks < 2; ++ks) {
-                  const unsigned long long ad = smemDesc(aAddr + t * A_TILE + sb * LEAF_STAGE + ks * KSTEP_A, KSTEP_A / 2, 128);
-                  const unsigned long long bd = smemDesc(lwAddr + ring * LW_STAGE + ks * KSTEP_BL, KSTEP_BL / 2, 128);
-                  mmaF16(tmem + t * 2 * NBLK, ad, bd, idescLeaf, (st | ks) ? 1u : 0u);
-                }
+                const unsigned long long ad = aDesc[t] + (unsigned)((sb * LEAF_STAGE) >> 4);
+                mmaF16(tmem + t * 2 * NBLK, ad, lwd, idescLeaf, st ? 1u : 0u);
+                mmaF16(tmem + t * 2 * NBLK, ad + (KSTEP_A >> 4), lwd + (KSTEP_BL >> 4), idescLeaf, 1u);
                 mmaCommit(bar(t * BAR_TILE + BAR_LEAFEMPTY + sb));
                 if (st == nst - 1) mmaCommit(bar(BAR_LEAFDONE + t));
               }
@@ -513,39 +615,53 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
             __syncwarp();
             ++lwCount;
           }
+          PROF_ADD(P_I_LEAF, tStep);
           continue;
         }
         const int nblk = s.numBlocks;
 #pragma unroll 1
         for (int nb = 0; nb < nblk && !failed; ++nb) {
           const unsigned ring = wCount % (unsigned)NB;
+          const long long tq = PROF_T();
           if (!w.wait(bar(BAR_WFULL + ring), (wCount / (unsigned)NB) & 1)) { failed = true; break; }
+          PROF_ADD(P_I_WAIT_WFULL, tq);
           const int b = nb & 1;
+          const unsigned long long bdBlock = bDesc0 + (unsigned)((ring * B_BLOCK) >> 4);
 #pragma unroll
           for (int t = 0; t < NTILE; ++t) {
             if (failed) break;
             if (nb == 0) {
-              if (!w.wait(bar(t * BAR_TILE + BAR_OPREADY), phOpReady[t])) { failed = true; break; }
-              phOpReady[t] ^= 1;
+              const long long tq4 = PROF_T();
+              unsigned& ph = t == 0 ? phOpReady0 : phOpReady1;
+              if (!w.wait(bar(t * BAR_TILE + BAR_OPREADY), ph)) { failed = true; break; }
+              PROF_ADD(P_I_WAIT_OPREADY, tq4);
+              ph ^= 1;
             } else if (nb >= 2) {
-              if (!w.wait(bar(t * BAR_TILE + BAR_ACCFREE + b), phAccFree[t][b])) { failed = true; break; }
-              phAccFree[t][b] ^= 1;
+              const long long tq5 = PROF_T();
+              unsigned& ph = t == 0 ? (b == 0 ? phAccFree00 : phAccFree01) : (b == 0 ? phAccFree10 : phAccFree11);
+              if (!w.wait(bar(t * BAR_TILE + BAR_ACCFREE + b), ph)) { failed = true; break; }
+              PROF_ADD(P_I_WAIT_ACCFREE, tq5);
+              ph ^= 1;
             }
             if (lane == 0) {
+              const long long tfz = PROF_T();
               fenceAfter();
+              PROF_ADD(P_I_FENCE, tfz);
+              const long long tmm = PROF_T();
               const unsigned d = tmem + t * 2 * NBLK + b * NBLK;
               // value x value, residue x value, value x residue, each over j 0..15 and j 16..31
 #pragma unroll
               for (int m = 0; m < 6; ++m) {
                 const int aks = (m < 4) ? m : m - 4;   // A k-step: 0,1 value; 2,3 residue; 0,1 value
                 const int bks = (m < 2) ? m : m - 2;   // B k-step: 0,1 value; 0,1 value; 2,3 residue
-                const unsigned long long ad = smemDesc(aAddr + t * A_TILE + aks * KSTEP_A, KSTEP_A / 2, 128);
-                const unsigned long long bd = smemDesc(bAddr + ring * B_BLOCK + bks * KSTEP_B, KSTEP_B / 2, 128);
-                mmaF16(d, ad, bd, idescSum, m ? 1u : 0u);
+                mmaF16(d, aDesc[t] + (unsigned)((aks * KSTEP_A) >> 4), bdBlock + (unsigned)((bks * KSTEP_B) >> 4), idescSum, m ? 1u : 0u);
               }
+              PROF_ADD(P_I_MMA, tmm);
+              const long long tcm = PROF_T();
               // self-test: leave out one commit, so that the workers' wait for it runs out
               if (!withheld) withheld = true;
               else mmaCommit(bar(t * BAR_TILE + BAR_ACCFULL + b));
+              PROF_ADD(P_I_COMMIT, tcm);
             }
             __syncwarp();
           }
@@ -553,8 +669,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
           __syncwarp();
           ++wCount;
         }
+        PROF_ADD(P_I_INNER, tStep);
       }
     }
+    PROF_ADD(P_I_TOTAL, tIs);
     // every MMA issued by this warp has completed when this barrier flips (also after a failure)
     if (lane == 0) mmaCommit(bar(BAR_DRAIN));
     __syncwarp();
@@ -563,6 +681,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
     // ================================ inner-region weight loader =====================================
     unsigned issued = 0;
     const unsigned bAddr = smemAddr(bring);
+    const long long tLs = PROF_T();
     for (unsigned long long pair = blockIdx.x; pair < npairs && !failed; pair += gridDim.x) {
       for (int si = 0; si < a.numSteps && !failed; ++si) {
         const DualStepDev s = a.steps[si];
@@ -571,7 +690,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
         for (int nb = 0; nb < s.numBlocks && !failed; ++nb) {
           const unsigned ring = issued % (unsigned)NB;
           // the slot's previous block has been multiplied for both tiles
+          const long long tq = PROF_T();
           if (issued >= (unsigned)NB && !w.wait(bar(BAR_WEMPTY + ring), ((issued / (unsigned)NB) - 1) & 1)) { failed = true; break; }
+          PROF_ADD(P_L_WAIT_WEMPTY, tq);
           if (lane == 0) {
             mbarExpectTx(bar(BAR_WFULL + ring), B_BLOCK);
             bulkLoad(bAddr + ring * B_BLOCK, src + (size_t)nb * B_BLOCK, B_BLOCK, bar(BAR_WFULL + ring));
@@ -581,6 +702,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
         }
       }
     }
+    PROF_ADD(P_L_TOTAL, tLs);
     // copies still in flight must land before the CTA's shared memory goes away
     const unsigned pending = issued < (unsigned)NB ? issued : (unsigned)NB;
     for (unsigned i = issued - pending; i < issued; ++i) w.wait(bar(BAR_WFULL + i % (unsigned)NB), (i / (unsigned)NB) & 1);
@@ -611,6 +733,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
 
   // ---- common exit: report, wait for the other roles' drains, free the tensor memory --------------------
   if (failed || *abortFlag) atomicExch(status, 1);
+  if (PROFILE && profOn) {
+    const int lo = tid == 0 ? 0 : (warp == 8 ? 16 : (warp == 9 ? 32 : 40)), hi = tid == 0 ? 16 : (warp == 8 ? 32 : (warp == 9 ? 40 : 48));
+    for (int i = lo; i < hi; ++i) profOut[i] = prof[i];
+  }
   fenceBefore();
   __syncthreads();
   if (warp == 0) {
@@ -629,13 +755,31 @@ int layeredDualThreads() { return NTHREADS; }
 
 cudaError_t layeredDualLaunch(const DualArgs& a, const float* xt, float* out, size_t n, int grid, size_t smem, int* status,
                               cudaStream_t stream) {
-  auto run = [&](auto kernel) -> cudaError_t {
+  auto run = [&](auto kernel, long long* prof) -> cudaError_t {
     cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(kernel), smem);
     if (e != cudaSuccess) return e;
-    kernel<<<grid, NTHREADS, smem, stream>>>(a, xt, out, (unsigned long long)n, status);
+    kernel<<<grid, NTHREADS, smem, stream>>>(a, xt, out, (unsigned long long)n, status, prof);
     return cudaGetLastError();
   };
-  return a.marginal ? run(layeredDualKernel<true>) : run(layeredDualKernel<false>);
+  if (std::getenv("SPNB_DUAL_PROFILE")) {
+    // development aid: per-phase cycle counts of the first CTA, printed after the launch (synchronous)
+    long long* dProf = nullptr;
+    if (cudaMalloc(&dProf, P_COUNT * sizeof(long long)) != cudaSuccess) return cudaErrorMemoryAllocation;
+    cudaMemset(dProf, 0, P_COUNT * sizeof(long long));
+    cudaError_t e = a.marginal ? run(layeredDualKernel<true, true>, dProf) : run(layeredDualKernel<false, true>, dProf);
+    long long h[P_COUNT];
+    cudaMemcpy(h, dProf, sizeof h, cudaMemcpyDeviceToHost);
+    cudaFree(dProf);
+    static const char* names[P_COUNT] = {"w_total", "w_leaf", "w_leaf_wait_empty", "w_leaf_wait_done", "w_inner", "w_inner_prep",
+        "w_inner_wait_full", "w_inner_fold", "w_deliver", "w_fold_ldwait", "w_leaf_build", "w_leaf_arrive", 0, 0, 0, 0,
+        "i_total", "i_wait_wfull", "i_wait_opready", "i_wait_accfree", "i_wait_lwfull", "i_wait_leaffull", "i_leaf", "i_inner", "i_mma", "i_commit", "i_fence", 0, 0, 0, 0, 0,
+        "l_total", "l_wait_wempty"};
+    std::fprintf(stderr, "[dual profile] n=%zu grid=%d:", n, grid);
+    for (int i = 0; i < P_COUNT; ++i) if (names[i]) std::fprintf(stderr, " %s=%lld", names[i], h[i]);
+    std::fprintf(stderr, "\n");
+    return e;
+  }
+  return a.marginal ? run(layeredDualKernel<true, false>, nullptr) : run(layeredDualKernel<false, false>, nullptr);
 }
 
 }  // namespace spnb

@@ -429,7 +429,7 @@ Plan buildPlan(const Model& m, bool logSpace) {
   }
   s.bytesPerSample = (int64_t)m.numFeatures * m.ftype.bytes() + (logSpace ? 4 : 8);
 
-  if (logSpace) buildProgram(p, INT32_MAX);
+  buildProgram(p, INT32_MAX);
   return p;
 }
 
@@ -442,6 +442,16 @@ void buildProgram(Plan& p, int32_t smemSlots) {
   const size_t n = d.size();
   const double LOG2E = 1.4426950408889634074;
   p.prog.clear();
+  p.progConsts.clear();
+  const bool lin = !p.logSpace;
+  std::map<uint64_t, int32_t> constIndex;   // equal constants share one table entry
+  auto constant = [&](double v) -> int32_t {
+    uint64_t bits;
+    std::memcpy(&bits, &v, 8);
+    auto ins = constIndex.emplace(bits, (int32_t)p.progConsts.size());
+    if (ins.second) p.progConsts.push_back(v);
+    return ins.first->second;
+  };
   std::vector<int64_t> lastUse(n, -1);
   for (size_t v = 0; v < n; ++v)
     for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) lastUse[d.childIdx[e]] = (int64_t)v;
@@ -474,6 +484,13 @@ void buildProgram(Plan& p, int32_t smemSlots) {
         p.prog.push_back(OP_GAUSS);
         p.prog.push_back(dst);
         p.prog.push_back(p.features[d.feature[v]].valueSlot);
+        if (lin) {
+          const double var = sd * sd;
+          p.prog.push_back(constant(d.mean[v]));
+          p.prog.push_back(constant(-1.0 / (2.0 * var)));
+          p.prog.push_back(constant(1.0 / std::sqrt(2.0 * M_PI * var)));
+          break;
+        }
         p.prog.push_back((int32_t)f32bits((float)d.mean[v]));
         p.prog.push_back((int32_t)f32bits((float)(-(1.0 / (2.0 * sd * sd)) * LOG2E)));
         p.prog.push_back((int32_t)f32bits((float)((-std::log(sd) - 0.5 * std::log(2 * M_PI)) * LOG2E)));
@@ -510,7 +527,7 @@ void buildProgram(Plan& p, int32_t smemSlots) {
         p.prog.push_back((int32_t)(hi - lo));
         for (int64_t e = lo; e < hi; ++e) {
           p.prog.push_back(slot[d.childIdx[e]]);
-          p.prog.push_back((int32_t)f32bits((float)std::log2(d.weight[e])));
+          p.prog.push_back(lin ? constant(d.weight[e]) : (int32_t)f32bits((float)std::log2(d.weight[e])));
         }
         break;
     }

@@ -87,11 +87,11 @@ struct PlanStats {
 };
 
 // Interpreter program: a flat int32 stream, all operands are value slots.
-//   OP_GAUSS  dst f  mu c2 c1            (floats bit-cast)
+//   OP_GAUSS  dst f  mu c2 c1            (floats bit-cast; linear space: indices of mean, exponent factor, coefficient)
 //   OP_TABLE  dst codeSlot lutOffset(-1: direct) tabOffset
 //   OP_HISTG  dst valueSlot brkOffset count tabOffset      (generic histogram)
 //   OP_PROD   dst k  s_0 .. s_{k-1}
-//   OP_SUM    dst k  (s_i w_i) * k        (w_i = log2 weight, bit-cast)
+//   OP_SUM    dst k  (s_i w_i) * k        (w_i = log2 weight, bit-cast; linear space: index of the weight)
 //   OP_END    src
 enum InterpOp : int32_t { OP_END = 0, OP_GAUSS = 1, OP_TABLE = 2, OP_PROD = 3, OP_SUM = 4, OP_HISTG = 5 };
 
@@ -112,6 +112,9 @@ struct Plan {
   PlanStats stats;
   // interpreter
   std::vector<int32_t> prog;
+  // linear-space programs name their constants by index into this table: OP_GAUSS carries (mean, -1/(2 var),
+  // 1/sqrt(2 pi var)) as three indices, OP_SUM one index per weight
+  std::vector<double> progConsts;
   std::vector<int32_t> groupBreaks; // breaks of the kGeneric groups
   int32_t numSlots = 0;       // slots needed when every value lives in shared memory
   int32_t numSmemSlots = 0;   // of the current program: shared-memory slots ...
