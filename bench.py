@@ -122,13 +122,23 @@ def cached_plan(cfg_id, spn, opts, workdir, rank=0):
     return query, plan_path, dt
 
 
-def warm_plan_cache(configs=(1, 2, 3, 4, 5)):
-    """Compile the bench plans into the cache (needs no GPU).  Called by __graft_entry__.build()."""
+def warm_plan_cache(configs=(1, 2, 3, 4, 5), prune=True):
+    """Compile the bench plans into the cache (needs no GPU) and drop plans made by an earlier build of the
+    library.  Called by __graft_entry__.build()."""
     import tempfile
+    keep = set()
     with tempfile.TemporaryDirectory() as wd:
         for c in configs:
             _, path, dt = cached_plan(c, make_model(c), compile_opts(c), wd)
+            if os.path.dirname(path) != PLAN_CACHE:      # compiled just now: the cache holds a copy
+                path = [os.path.join(PLAN_CACHE, f) for f in os.listdir(PLAN_CACHE) if f.startswith("cfg%d_" % c)]
+                path = max(path, key=os.path.getmtime)
+            keep.add(os.path.basename(path))
             print("plan cache: cfg%d %s (%.1f s)" % (c, os.path.basename(path), dt), flush=True)
+    if prune and os.path.isdir(PLAN_CACHE):
+        for f in os.listdir(PLAN_CACHE):
+            if f not in keep:
+                os.remove(os.path.join(PLAN_CACHE, f))
 
 
 class ClockSampler:

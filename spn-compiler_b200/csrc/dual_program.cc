@@ -52,11 +52,11 @@ bool buildDualProgram(const LayeredPlan& lp, const std::vector<long long>& fragO
       d.featOffset = (int)s.featOffset;
       d.paramOffset = (long long)s.paramOffset;
       if (fragOffset[i] >= 0) {
-        const int nst = (s.numFeatures + 3) / 4, nstPad = (nst + 3) / 4 * 4;
+        const int nst = (s.numFeatures + 7) / 8;
         d.numBlocks = nst;
         d.fragOffset = fragOffset[i] * 8;
-        d.stageBase = (int)(out->cols4.size() / 4);
-        for (int q = 0; q < nstPad * 4; ++q) {
+        d.stageBase = (int)(out->cols4.size() / 8);
+        for (int q = 0; q < nst * 8; ++q) {
           out->cols4.push_back(q < s.numFeatures ? lp.features[(size_t)s.featOffset + q] : 0);
           out->centres4.push_back(q < s.numFeatures ? centres[(size_t)s.featOffset + q] : 0.f);
         }
@@ -91,7 +91,7 @@ std::string dualProgramSummary(const DualProgram& p) {
   // one letter per step: leaf / inner / root part in upper case, followed by the destination (s<slot>, o, r, -)
   // and, for inner steps, the source of the left operand (<slot> or r)
   std::ostringstream o;
-  o << "{\"a_slots\":" << p.aSlots << ",\"leaf_stages\":" << p.cols4.size() / 4 << ",\"steps\":\"";
+  o << "{\"a_slots\":" << p.aSlots << ",\"leaf_stages\":" << p.cols4.size() / 8 << ",\"steps\":\"";
   for (const DualStepDev& d : p.steps) {
     o << (d.op == kLeafRegion ? 'L' : (d.op == kInnerRegion ? 'I' : 'R'));
     if (d.op != kLeafRegion) {

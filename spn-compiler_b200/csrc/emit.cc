@@ -56,9 +56,9 @@ std::string max3Tree(const std::vector<std::string>& t, size_t lo, size_t hi) {
 
 // Bytes of the code -> bucket byte tables the generated kernel reads: none if every table-driven group's
 // buckets are computed arithmetically.
-static size_t lutBytesNeeded(const Plan& p, const EmitOptions& opt) {
+static size_t lutBytesNeeded(const Plan& p, const EmitOptions& opt, bool clamp) {
   for (const IndexGroup& g : p.groups)
-    if (g.mode == kLut && !(g.arith && opt.bucketArith)) return p.lut.size();
+    if (g.mode == kLut && !(g.arith && opt.bucketArith) && !(clamp && p.features[g.feature].clampCodes)) return p.lut.size();
   return 0;
 }
 
@@ -79,14 +79,18 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   int maxDomain = 0;
   for (const FeatureMeta& fm : p.features)
     if (fm.codeSlot >= 0) maxDomain = std::max(maxDomain, fm.domain);
-  const int cb = maxDomain + 2 <= 255 ? 1 : 2;
+  // arithmetic buckets with clamped special codes: the missing-input code 65535 needs 16-bit codes
+  const bool clampAllowed = opt.bucketClamp;
+  bool anyClamp = false;
+  for (const FeatureMeta& fm : p.features) anyClamp = anyClamp || (clampAllowed && fm.clampCodes);
+  const int cb = (maxDomain + 2 <= 255 && !anyClamp) ? 1 : 2;
   const size_t tabBytes = tabEntries * realBytes;
   size_t tableLimit = (size_t)opt.smemTableLimit;
   if (TILE <= 0) {
     const bool nanFlags = p.marginal && p.ftype.isFloat() && p.numValueSlots > 0 && p.stats.gauss > 0;
     const size_t perThread = (size_t)p.numValueSlots * realBytes + (size_t)p.numCodeSlots * cb + (nanFlags ? 4 : 0);
     size_t fixed = (size_t)d.numFeatures * 16 + 64;
-    if (lutBytesNeeded(p, opt) <= (size_t)opt.smemTableLimit) fixed += lutBytesNeeded(p, opt);
+    if (lutBytesNeeded(p, opt, clampAllowed) <= (size_t)opt.smemTableLimit) fixed += lutBytesNeeded(p, opt, clampAllowed);
     const size_t budget = 226 * 1024;  // one CTA may use up to 227 KB
     bool found = false;
     // candidates in steps of a warp below 512 threads: with 1 KB of staged inputs per sample the difference
@@ -112,9 +116,11 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // ---- scope-local staging (see EmitOptions::scoped) ---------------------------------------------------
   // DAGs up to one and a half chunk sizes stay in one function; larger ones are cut into equal stretches
   size_t chunkNodes = opt.chunkNodes > 0 ? (size_t)opt.chunkNodes : n;
-  if (n <= chunkNodes + chunkNodes / 2) chunkNodes = n;
-  else chunkNodes = (n + (n + chunkNodes - 1) / chunkNodes - 1) / ((n + chunkNodes - 1) / chunkNodes);
-  const bool scopedPossible = lg && p.ftype.isFloat() && p.ftype.bits == 32 && opt.groupTiles <= 1;
+  if (!opt.chunkExact) {
+    if (n <= chunkNodes + chunkNodes / 2) chunkNodes = n;
+    else chunkNodes = (n + (n + chunkNodes - 1) / chunkNodes - 1) / ((n + chunkNodes - 1) / chunkNodes);
+  }
+  const bool scopedPossible = lg && p.ftype.isFloat() && p.ftype.bits == 32;
   const bool scoped = scopedPossible &&
                       (opt.scoped == 1 || (opt.scoped < 0 && opt.tile <= 0 && TILE < 1024 && n > chunkNodes));
   if (scoped) {
@@ -134,7 +140,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const int NV = p.numValueSlots, NC = p.numCodeSlots;
   bool identity = (NC == 0 && NV == F) && !scoped;
   for (int f = 0; identity && f < F; ++f) identity = p.features[f].valueSlot == f;
-  const size_t lutBytes = lutBytesNeeded(p, opt);
+  const size_t lutBytes = lutBytesNeeded(p, opt, clampAllowed);
   const bool lutSmem = lutBytes > 0 && lutBytes <= (size_t)opt.smemTableLimit;
   // ---- asynchronous double-buffered staging (see EmitOptions::asyncStage) -----------------------------------
   const int RS = F | 1;                                      // row stride in words: odd, conflict-free
@@ -161,48 +167,82 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     const size_t fixed = 64 + std::min(tabBytes, tableLimit) + 16 + (lutSmem ? p.lut.size() + 4 : 0);
     scopeBudget = (226 * 1024 - fixed) / (size_t)TILE - (nanFlagsWanted ? 4 : 0);
     if (opt.scopeBytes > 0) scopeBudget = std::min<size_t>(scopeBudget, (size_t)opt.scopeBytes);
-    std::vector<int32_t> vstamp(F, -1), cstamp(F, -1), vslotOf(F, -1), cslotOf(F, -1);
-    chunkValueFeat.emplace_back();
-    chunkCodeFeat.emplace_back();
-    int32_t cur = 0;
-    size_t bytes = 0;
-    for (size_t v = 0; v < n; ++v) {
-      int32_t needValue = -1, needCode = -1;
+    // Values alive across position q (defined before q, used at or after q): what a cut at q sends through
+    // the scratch area.  A chunk is grown until its leaves would need more staged bytes than fit (or it has
+    // chunkNodes nodes); the cut is then placed at the position of its second half where the fewest values
+    // cross, which is where one sub-DAG ends and the next begins in the depth-first evaluation order.
+    std::vector<int32_t> crossing(n + 1, 0);
+    {
+      std::vector<int64_t> last(n, -1);
+      for (size_t v = 0; v < n; ++v)
+        for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) last[d.childIdx[e]] = (int64_t)v;
+      std::vector<int32_t> diff(n + 2, 0);
+      for (size_t u = 0; u < n; ++u)
+        if (last[u] > (int64_t)u) { diff[u + 1]++; diff[(size_t)last[u] + 1]--; }   // alive at positions u+1 .. last[u]
+      int32_t run = 0;
+      for (size_t q = 0; q <= n; ++q) { run += diff[q]; crossing[q] = run; }
+    }
+    auto needOf = [&](size_t v, int32_t& needValue, int32_t& needCode) {
+      needValue = needCode = -1;
       if (d.kind[v] == kGaussian) needValue = d.feature[v];
       else if (d.kind[v] == kCategorical || d.kind[v] == kHistogram) {
         const IndexGroup& G = p.groups[d.group[v]];
         if (G.mode == kGeneric) needValue = G.feature; else needCode = G.feature;
       }
-      size_t add = 0;
-      if (needValue >= 0 && vstamp[needValue] != cur) add = 4;
-      if (needCode >= 0 && cstamp[needCode] != cur) add = (size_t)cb;
-      if (add > scopeBudget) add = scopeBudget;   // a budget smaller than one feature still makes progress
-      if ((bytes + add > scopeBudget && bytes > 0) || v - chunkStart.back() >= chunkNodes) {
-        chunkStart.push_back(v);
-        chunkValueFeat.emplace_back();
-        chunkCodeFeat.emplace_back();
-        ++cur;
-        bytes = 0;
+    };
+    std::vector<int32_t> vstamp(F, -1), cstamp(F, -1), vslotOf(F, -1), cslotOf(F, -1);
+    chunkStart.clear();
+    int32_t cur = 0, stamp = 0;
+    size_t begin = 0;
+    while (begin < n) {
+      // how far the budget reaches
+      ++stamp;
+      size_t bytes = 0, reach = begin;
+      for (; reach < n && reach - begin < chunkNodes; ++reach) {
+        int32_t nv, nc;
+        needOf(reach, nv, nc);
+        size_t add = 0;
+        if (nv >= 0 && vstamp[nv] != stamp) add = 4;
+        if (nc >= 0 && cstamp[nc] != stamp) add = (size_t)cb;
+        if (bytes + add > scopeBudget && reach > begin) break;
+        if (nv >= 0) vstamp[nv] = stamp;
+        if (nc >= 0) cstamp[nc] = stamp;
+        bytes += add;
       }
-      chunkOf[v] = cur;
-      if (needValue >= 0) {
-        if (vstamp[needValue] != cur) {
-          vstamp[needValue] = cur;
-          vslotOf[needValue] = (int32_t)chunkValueFeat.back().size();
-          chunkValueFeat.back().push_back(needValue);
-          bytes += 4;
+      size_t cut = reach;
+      if (reach < n) {
+        const size_t lo = begin + std::max<size_t>(1, (reach - begin) / 2);
+        for (size_t q = lo; q <= reach; ++q)
+          if (crossing[q] <= crossing[cut]) cut = q;
+      }
+      // the chunk [begin, cut): its staged features and the slot every leaf reads
+      chunkStart.push_back(begin);
+      chunkValueFeat.emplace_back();
+      chunkCodeFeat.emplace_back();
+      ++stamp;
+      for (size_t v = begin; v < cut; ++v) {
+        chunkOf[v] = cur;
+        int32_t nv, nc;
+        needOf(v, nv, nc);
+        if (nv >= 0) {
+          if (vstamp[nv] != stamp) {
+            vstamp[nv] = stamp;
+            vslotOf[nv] = (int32_t)chunkValueFeat.back().size();
+            chunkValueFeat.back().push_back(nv);
+          }
+          leafSlot[v] = vslotOf[nv];
         }
-        leafSlot[v] = vslotOf[needValue];
-      }
-      if (needCode >= 0) {
-        if (cstamp[needCode] != cur) {
-          cstamp[needCode] = cur;
-          cslotOf[needCode] = (int32_t)chunkCodeFeat.back().size();
-          chunkCodeFeat.back().push_back(needCode);
-          bytes += (size_t)cb;
+        if (nc >= 0) {
+          if (cstamp[nc] != stamp) {
+            cstamp[nc] = stamp;
+            cslotOf[nc] = (int32_t)chunkCodeFeat.back().size();
+            chunkCodeFeat.back().push_back(nc);
+          }
+          leafSlot[v] = cslotOf[nc];
         }
-        leafSlot[v] = cslotOf[needCode];
       }
+      ++cur;
+      begin = cut;
     }
     for (size_t c = 0; c < chunkValueFeat.size(); ++c)
       maxStageBytes = std::max(maxStageBytes, chunkValueFeat[c].size() * 4 + chunkCodeFeat[c].size() * (size_t)cb);
@@ -242,7 +282,9 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "// per feature: lo, domain, code slot, value slot\n__device__ const int FM[NF * 4] = {";
     for (int f = 0; f < F; ++f) {
       const FeatureMeta& fm = p.features[f];
-      o << (f ? "," : "") << fm.lo << "," << fm.domain << "," << fm.codeSlot << "," << fm.valueSlot;
+      // (code slot + 65536: the feature's special codes are the clamped ones, see FeatureMeta::clampCodes)
+      o << (f ? "," : "") << fm.lo << "," << fm.domain << ","
+        << (fm.codeSlot >= 0 && clampAllowed && fm.clampCodes ? fm.codeSlot + 65536 : fm.codeSlot) << "," << fm.valueSlot;
     }
     o << "};\n";
   }
@@ -313,6 +355,13 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     const int valueSlot = scoped ? leafSlot[v] : (asyncStage ? G.feature : fm.valueSlot);
     if (G.mode == kDirect) {
       out << readCode(c, codeSlot, (long long)v) << readTab(name, p.tabOffset[v], c, (long long)v);
+    } else if (G.mode == kLut && clampAllowed && fm.clampCodes) {
+      // bucket = min((code * mul + add) >> 16, count + 1): the staged special codes land on the two entries
+      // behind the buckets by themselves
+      const std::string b = "b" + std::to_string(v);
+      out << readCode(c, codeSlot, (long long)v);
+      out << "  const int " << b << " = min((" << c << " * " << G.clMul << " + " << G.clAdd << ") >> 16, " << (G.count + 1) << ");\n";
+      out << readTab(name, p.tabOffset[v], b, (long long)v);
     } else if (G.mode == kLut && G.arith && opt.bucketArith) {
       // bucket computed from the code; codes 0 (missing input) and 1 (outside the domain) select the two
       // entries behind the buckets
@@ -392,6 +441,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // tiles per group: 1 = each tile runs all chunks; more = each chunk runs on that many tiles in a row
   // (measured on a 53 k-node DAG: grouping is slower than streaming every chunk once per tile, so the
   // default stays 1)
+  // (measured on the 53 k-node DAG with scope-local staging: 86.8 ms with one tile per chunk run, 96.0 with two,
+  // 125.1 with four: every run reloads the table window, and the code is not what the kernel waits for)
   const int groupTiles = nChunks > 1 && opt.groupTiles > 0 ? opt.groupTiles : 1;
   const char* ldGlobal = lg ? "ld.global.f32" : "ld.global.f64";
   const char* stGlobal = lg ? "st.global.f32" : "st.global.f64";
@@ -411,6 +462,23 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   if (streamed && (chunk == 0 || groupTiles > 1)) swapWindow(o, winBase);
   std::vector<uint8_t> loaded(nChunks > 1 ? n : 0, 0);
   std::vector<std::string> terms;
+  if (scoped && nChunks > 1) {
+    // Operands defined by earlier chunks: when they are few, all of them are requested at the top of the
+    // function, so that their latencies (L2 or DRAM) overlap instead of standing in front of every first use.
+    std::vector<int32_t> incoming;
+    for (size_t v = v0; v < v1; ++v)
+      for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
+        const int32_t c = d.childIdx[e];
+        if ((size_t)c < v0 && !loaded[c]) { loaded[c] = 1; incoming.push_back(c); }
+      }
+    if (incoming.size() <= 24) {
+      for (int32_t c : incoming)
+        o << "  real_t " << V(c) << "; asm volatile(\"" << ldGlobal << " %0, [%1+" << (long long)crossSlot[c] * TILE * rb
+          << "];\" : \"=" << cReal << "\"(" << V(c) << ") : \"l\"(sc) : \"memory\");\n";
+    } else {
+      for (int32_t c : incoming) loaded[c] = 0;
+    }
+  }
   for (size_t v = v0; v < v1; ++v) {
     // operands defined by an earlier chunk are fetched from the scratch area on first use
     if (nChunks > 1)
@@ -526,7 +594,12 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     for (size_t c = 0; c < nChunks; ++c) {
       cfOff[c] = cfN;
       for (int32_t f : chunkValueFeat[c]) { o << (cfN ? "," : "") << f; ++cfN; }
-      for (int32_t f : chunkCodeFeat[c]) { o << (cfN ? "," : "") << f << "," << p.features[f].lo << "," << p.features[f].domain; cfN += 3; }
+      // (domain stored as -domain - 1: the feature's special codes are the clamped ones)
+      for (int32_t f : chunkCodeFeat[c]) {
+        const FeatureMeta& fm = p.features[f];
+        o << (cfN ? "," : "") << f << "," << fm.lo << "," << (clampAllowed && fm.clampCodes ? -fm.domain - 1 : fm.domain);
+        cfN += 3;
+      }
     }
     if (!cfN) o << "0";
     o << "};\n";
@@ -543,13 +616,16 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "  for (int j = 0; j < nc; ++j) {\n";
     o << "    const float raw = src[(unsigned long long)__ldg(cf + 3 * j) * ld];\n";
     o << "    const unsigned rr = (unsigned)TOINT(raw) - (unsigned)__ldg(cf + 3 * j + 1);\n";
-    o << "    int code = rr < (unsigned)__ldg(cf + 3 * j + 2) ? (int)rr + 2 : 1;\n";
-    o << "    if (raw != raw) code = 0;\n";
+    o << "    const int dm = __ldg(cf + 3 * j + 2);\n";
+    o << "    const bool cl = dm < 0;\n";
+    o << "    const int dom = cl ? -dm - 1 : dm;\n";
+    o << "    int code = rr < (unsigned)dom ? (int)rr + 2 : (cl ? dom + 2 : 1);\n";
+    o << "    if (raw != raw) code = cl ? 65535 : 0;\n";
     o << "    cs[j * SX + tid] = (code_t)code;\n";
     o << "  }\n  return nan;\n}\n";
     o << "extern \"C\" __global__ void __launch_bounds__(TILE, 1)\n";
     o << "spnb_kernel(const float* __restrict__ xt, out_t* __restrict__ out, unsigned long long n, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, real_t* __restrict__ scratch, unsigned long long ld)\n{\n";
-    if (nCross > 0) o << "  real_t* sc = scratch + ((size_t)blockIdx.x * " << (size_t)nCross << "u * TILE + threadIdx.x);\n";
+    if (nCross > 0) o << "  real_t* sc = scratch + ((size_t)blockIdx.x * " << (size_t)nCross * (size_t)groupTiles << "u * TILE + threadIdx.x);\n";
     else o << "  real_t* sc = scratch;\n";
     o << "  extern __shared__ __align__(16) unsigned char smem_raw[];\n";
     o << "  const unsigned tid = threadIdx.x;\n";
@@ -565,32 +641,49 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       o << "    for (unsigned i = tid; i < NLUT; i += TILE) lut[i] = lut_g[i];\n    lut_s = (unsigned)__cvta_generic_to_shared(lut); }\n";
     }
     o << "  const unsigned long long ntiles = (n + TILE - 1) / TILE;\n";
+    // Every chunk runs on groupTiles tiles in a row (each with its own slice of the cross-chunk scratch), so
+    // that its code, which fits the instruction cache, is fetched once per group instead of once per tile.
+    // (a batch with fewer tiles than that per CTA is cut into smaller groups, so that every CTA gets work)
+    o << "  unsigned G = (unsigned)(ntiles / gridDim.x);\n";
+    o << "  G = G < 1u ? 1u : (G > " << groupTiles << "u ? " << groupTiles << "u : G);\n";
+    o << "  const unsigned long long ngroups = (ntiles + G - 1) / G;\n";
     o << "#pragma unroll 1\n";
-    o << "  for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
-    o << "    const unsigned long long base = tile * TILE;\n";
-    o << "    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
-    o << "    // threads past the end of the batch repeat its last sample; their result is not stored\n";
-    o << "    const float* __restrict__ src = xt + base + (tid < rows ? tid : rows - 1);\n";
-    o << "    out_t res = (out_t)0;\n";
+    o << "  for (unsigned long long group = blockIdx.x; group < ngroups; group += gridDim.x) {\n";
     for (size_t c = 0; c < nChunks; ++c) {
       const size_t nv = chunkValueFeat[c].size(), nc = chunkCodeFeat[c].size();
-      o << "    {  // chunk " << c << ": " << nv << " staged values, " << nc << " staged codes\n";
+      o << "    // chunk " << c << ": " << nv << " staged values, " << nc << " staged codes\n";
+      o << "#pragma unroll 1\n";
+      o << "    for (unsigned t = 0; t < G; ++t) {\n";
+      o << "      const unsigned long long tile = group * G + t;\n";
+      o << "      if (tile >= ntiles) break;\n";
+      o << "      const unsigned long long base = tile * TILE;\n";
+      o << "      const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
+      o << "      // threads past the end of the batch repeat its last sample; their result is not stored\n";
+      o << "      const float* __restrict__ src = xt + base + (tid < rows ? tid : rows - 1);\n";
+      o << "      real_t* sct = sc + (size_t)t * " << nCross << "u * TILE;\n";
       o << "      __syncthreads();\n";
       const bool choose = twoBodies && nv > 0;
       o << "      " << (choose ? "const int nan = " : "") << "spnb_stage(smem_raw, src, ld, CF + " << cfOff[c] << ", " << nv << ", " << nc << ", "
         << codeBase(c) << "u, tid);\n";
-      const std::string args = "(xs_s, xs_s + " + std::to_string(codeBase(c)) + "u, tab_s, lut_s, tab_g, lut_g, win, sc, tid);\n";
-      const std::string lhs = c + 1 == nChunks ? "res = " : "";
+      const std::string args = "(xs_s, xs_s + " + std::to_string(codeBase(c)) + "u, tab_s, lut_s, tab_g, lut_g, win, sct, tid);\n";
+      const bool last = c + 1 == nChunks;
+      const std::string lhs = last ? "const out_t res = " : "";
       if (choose) {
-        o << "      if (__syncthreads_or(nan)) " << lhs << "spnb_body_nan" << c << args;
-        o << "      else " << lhs << "spnb_body" << c << args;
+        if (last) {
+          o << "      out_t res;\n";
+          o << "      if (__syncthreads_or(nan)) res = spnb_body_nan" << c << args;
+          o << "      else res = spnb_body" << c << args;
+        } else {
+          o << "      if (__syncthreads_or(nan)) spnb_body_nan" << c << args;
+          o << "      else spnb_body" << c << args;
+        }
       } else {
         o << "      __syncthreads();\n";
         o << "      " << lhs << "spnb_body" << c << args;
       }
+      if (last) o << "      if (tid < rows) out[base + tid] = res;\n";
       o << "    }\n";
     }
-    o << "    if (tid < rows) out[base + tid] = res;\n";
     o << "  }\n}\n";
     if (info) {
       info->kernelName = "spnb_kernel";
@@ -599,7 +692,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       info->tablesInSmem = tabSmem;
       info->tableEntries = tabEntries;
       info->dynamicSmemBytes = smemTotal;
-      info->scratchSlots = nCross;
+      info->scratchSlots = nCross * groupTiles;
       info->scoped = true;
       info->numChunks = (int)nChunks;
     }
@@ -727,9 +820,17 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       if (NC) {
         o << ind << "    if (m.z >= 0) {\n";
         o << ind << "      const unsigned rr = (unsigned)TOINT(raw) - (unsigned)m.x;\n";
-        o << ind << "      int code = rr < (unsigned)m.y ? (int)rr + 2 : 1;\n";
-        if (floatIn) o << ind << "      if (raw != raw) code = 0;\n";
-        o << ind << "      cs[m.z * SX + r] = (code_t)(live ? code : 1);\n";
+        if (anyClamp) {
+          o << ind << "      const bool cl = m.z >= 65536;\n";
+          o << ind << "      const int oor = cl ? m.y + 2 : 1;\n";
+          o << ind << "      int code = rr < (unsigned)m.y ? (int)rr + 2 : oor;\n";
+          if (floatIn) o << ind << "      if (raw != raw) code = cl ? 65535 : 0;\n";
+          o << ind << "      cs[(m.z & 65535) * SX + r] = (code_t)(live ? code : oor);\n";
+        } else {
+          o << ind << "      int code = rr < (unsigned)m.y ? (int)rr + 2 : 1;\n";
+          if (floatIn) o << ind << "      if (raw != raw) code = 0;\n";
+          o << ind << "      cs[m.z * SX + r] = (code_t)(live ? code : 1);\n";
+        }
         o << ind << "    }\n";
       }
       o << ind << "  }\n";

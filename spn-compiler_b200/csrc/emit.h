@@ -15,10 +15,15 @@ struct EmitOptions {
                            // on the same stretch of the instruction stream
   int gaussForm = 1;       // 1: fma(d, d, c1/c2) * c2 (three instructions); 0: fma(d*d, c2, c1)
   int chunkNodes = 2000;   // DAG nodes per generated function (0: one function)
+  bool chunkExact = false; // the caller asked for that size (spnb-chunk-nodes, maxTaskSize): a hard cap; otherwise DAGs
+                           // up to one and a half chunk sizes stay in one function and larger ones are cut evenly
   int groupTiles = 0;      // chunked kernels: tiles a chunk runs on back to back (0 or 1: each tile runs all chunks)
   bool useMax3 = true;     // three-input max.f32 (needs a JIT that knows PTX ISA 8.8)
   bool bucketArith = false;  // histogram buckets by multiply-shift where that reproduces the byte table exactly
                              // (off: five ALU instructions per leaf cost more than the shared-memory read they save)
+  bool bucketClamp = false;  // ... with the special codes staged so that one clamp replaces the special cases: three
+                             // integer instructions instead of a shared-memory read (measured on the 100-feature
+                             // histogram model: 8.43 ms either way, so the byte table stays the default)
   int smemTableLimit = 64 * 1024;  // shared-memory window for leaf tables; larger tables are streamed through it
   // Scope-local staging.  When the inputs of 1024 samples do not fit into shared memory at once (hundreds of
   // features), the DAG is cut into chunks whose leaves read few enough features, and every chunk stages only

@@ -218,6 +218,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-interp-slots") o.interpSlots = std::atoi(v.c_str());
     else if (k == "spnb-mma-split") o.mmaSplit = std::atoi(v.c_str());
     else if (k == "spnb-bucket-arith") o.bucketArith = std::atoi(v.c_str());
+    else if (k == "spnb-bucket-clamp") o.bucketClamp = std::atoi(v.c_str());
     else if (k == "spnb-tc-warpgroups") {
       o.tcWarpgroups = std::atoi(v.c_str());
       if (o.tcWarpgroups != 1 && o.tcWarpgroups != 2 && o.tcWarpgroups != 4) fail("spnb-tc-warpgroups must be 1, 2 or 4");
@@ -228,6 +229,13 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-tc-tiles") {
       o.tcTiles = std::atoi(v.c_str());
       if (o.tcTiles != 1 && o.tcTiles != 2) fail("spnb-tc-tiles must be 1 or 2");
+    } else if (k == "spnb-tc-rings") {
+      o.tcRings = std::atoi(v.c_str());
+      if (o.tcRings != 0 && o.tcRings != 44 && o.tcRings != 43 && o.tcRings != 42 && o.tcRings != 33 && o.tcRings != 32)
+        fail("spnb-tc-rings must be 0 (automatic), 44, 43, 42, 33 or 32 (weight blocks and leaf stages in flight)");
+    } else if (k == "spnb-tc-fold") {
+      if (v != "packed" && v != "scalar") fail("spnb-tc-fold must be packed or scalar");
+      o.tcFoldScalar = v == "scalar" ? 1 : 0;
     } else if (k == "spnb-spin-limit") {
       o.spinLimit = std::atoll(v.c_str());
       if (o.spinLimit < 0 || o.spinLimit > (1ll << 30)) fail("spnb-spin-limit must be between 0 and 2^30");
@@ -281,12 +289,13 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     // graph into tasks of at most maxTaskSize operations that hand their results on through [k x N] buffers
     // in global memory.  The equivalent here: functions of at most that many DAG nodes over consecutive
     // stretches of the evaluation order, results crossing a cut through the per-CTA scratch area.
-    if (opt.maxTaskSize > 0) eo.chunkNodes = opt.maxTaskSize;
-    if (opt.chunkNodes >= 0) eo.chunkNodes = opt.chunkNodes;
+    if (opt.maxTaskSize > 0) { eo.chunkNodes = opt.maxTaskSize; eo.chunkExact = true; }
+    if (opt.chunkNodes >= 0) { eo.chunkNodes = opt.chunkNodes; eo.chunkExact = true; }
     eo.groupTiles = opt.groupTiles;
     if (opt.tableWindow) eo.smemTableLimit = std::min(std::max(opt.tableWindow, 1024), 160 * 1024);
     eo.useMax3 = jitVersion() >= 1209;
     eo.bucketArith = opt.bucketArith != 0;
+    eo.bucketClamp = opt.bucketClamp != 0;
     eo.scoped = opt.scoped;
     eo.asyncStage = opt.asyncStage;
     eo.scopeBytes = opt.scopeBytes;
@@ -385,6 +394,7 @@ struct Engine::DeviceState {
   void* dDualSteps = nullptr;
   void* dDualCols = nullptr;
   void* dDualCentres = nullptr;
+  void* dDualScaleMul = nullptr;
   int samplesPerCta = 0;     // samples one CTA takes per step of its tile loop, if not the block size
   size_t layeredChunkRows = 0;   // samples copied feature-major at a time (layered kernels, scoped generated kernels)
   size_t crossBytes = 0;         // scoped generated kernels: bytes of cross-chunk scratch in front of that copy
@@ -434,6 +444,7 @@ struct Engine::DeviceState {
     if (dDualSteps) cudaFree(dDualSteps);
     if (dDualCols) cudaFree(dDualCols);
     if (dDualCentres) cudaFree(dDualCentres);
+    if (dDualScaleMul) cudaFree(dDualScaleMul);
     if (module) Driver::get().moduleUnload(module);
   }
 };
@@ -476,6 +487,8 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->tcTiles_ = opt.tcTiles;
   if (opt.spinLimit > 0) e->spinLimit_ = (unsigned)opt.spinLimit;
   e->selftestWithhold_ = opt.selftestWithhold;
+  e->tcFoldScalar_ = opt.tcFoldScalar;
+  e->tcRings_ = opt.tcRings;
   // layered models run on the tensor-memory kernel unless another layered kernel is asked for by name
   e->layeredTcf_ = opt.kernelMode != "layered-scalar" && opt.kernelMode != "layered-mma";
   e->meta_.kernelName = e->model_.name;
@@ -775,35 +788,57 @@ Engine::DeviceState& Engine::state(int device) {
             std::vector<float>& centres4 = prog.centres4;
             const size_t ns = ds.size();
             const int maxDepth = prog.aSlots, depth = 0;
-            int ring = 0;
-            for (int cand : {4, 3})
-              if (!ring && layeredDualSmemBytes(std::max(maxDepth, 1), cand) <= (size_t)prop.sharedMemPerBlockOptin) ring = cand;
+            // Ring depths (weight blocks, leaf stages in flight): the deepest pair that fits, or the one asked for.
+            // With three or more pending left operands the outermost one (written and read once per repetition)
+            // is kept in global memory, which buys the rings 33 KB of shared memory.
+            int ring = 0, leafRing = 0;
+            const int globalSlots = maxDepth >= 3 ? 1 : 0;
+            const int smemSlots = std::max(maxDepth - globalSlots, 1);
+            static const int kRings[][2] = {{4, 4}, {4, 3}, {4, 2}, {3, 3}, {3, 2}};
+            for (auto& cand : kRings) {
+              if (ring) break;
+              if (tcRings_ > 0 && (cand[0] != tcRings_ / 10 || cand[1] != tcRings_ % 10)) continue;
+              if (layeredDualSmemBytes(smemSlots, cand[0], cand[1]) <= (size_t)prop.sharedMemPerBlockOptin) {
+                ring = cand[0];
+                leafRing = cand[1];
+              }
+            }
             if (ring && depth == 0) {
-              if (cols4.empty()) { cols4.assign(4, 0); centres4.assign(4, 0.f); }
+              if (cols4.empty()) { cols4.assign(8, 0); centres4.assign(8, 0.f); }
+              // per sum the largest weight of its row, the multiplier form of the log2 scales
+              std::vector<float> scaleMul(scales.size());
+              for (size_t q = 0; q < scales.size(); ++q) scaleMul[q] = std::isfinite(scales[q]) ? std::exp2(scales[q]) : 0.f;
+              st->dDualScaleMul = upload(scaleMul.data(), scaleMul.size() * 4);
+              st->da.scaleMul = (const float*)st->dDualScaleMul;
+              st->da.leafRing = leafRing;
               st->dDualSteps = upload(ds.data(), ds.size() * sizeof(DualStepDev));
               st->dDualCols = upload(cols4.data(), cols4.size() * 4);
               st->dDualCentres = upload(centres4.data(), centres4.size() * 4);
               st->da.steps = (const DualStepDev*)st->dDualSteps;
               st->da.numSteps = (int)ns;
-              st->da.aSlots = std::max(maxDepth, 1);
+              st->da.aSlots = smemSlots;
+              st->da.globalSlots = globalSlots;
               st->da.ringBlocks = ring;
               st->da.marginal = st->la.marginal;
               st->da.frags = (const unsigned char*)st->dFrags;
               st->da.scales = (const float*)st->dScales;
               st->da.leafCols = (const int*)st->dDualCols;
               st->da.leafCentres = (const float*)st->dDualCentres;
-              st->da.numLeafStages = (int)(cols4.size() / 4);
+              st->da.numLeafStages = (int)(cols4.size() / 8);
               st->da.features = st->la.features;
               st->da.leafParams = st->la.leafParams;
               st->da.spinLimit = spinLimit_;
               st->da.testWithholdCommit = selftestWithhold_;
+              st->da.foldScalar = tcFoldScalar_;
               st->useDual = true;
               st->block = layeredDualThreads();
               st->samplesPerCta = 256;
-              st->smem = layeredDualSmemBytes(st->da.aSlots, ring);
+              st->smem = layeredDualSmemBytes(st->da.aSlots, ring, leafRing);
               st->grid = st->smCount;   // one CTA per SM: the kernel owns the SM's tensor memory
               st->layeredChunkRows = 512 * 1024;
-              st->scratchBytes = st->layeredChunkRows * (size_t)p.features.size() * 4;
+              // scratch per stream: the spilled a-stack slots of every CTA, then the feature-major input copy
+              st->crossBytes = (layeredDualGlobalStackBytes(st->grid, globalSlots) + 255) & ~size_t(255);
+              st->scratchBytes = st->crossBytes + st->layeredChunkRows * (size_t)p.features.size() * 4;
               auto insD = dev_.emplace(device, std::move(st));
               return *insD.first->second;
             }
@@ -949,7 +984,7 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
         void* dst = (char*)dOut + r0 * resBytes;
         CUDA_OK(transposeInputs(dtypeCode(plan_.ftype), src, xt, rows, (int)meta_.numFeatures, ld, stream));
         const size_t tilesC = (rows + (size_t)st.block - 1) / (size_t)st.block;
-        const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);
+        const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);   // groups of tiles stride over the grid
         void* args[] = {(void*)&xt, (void*)&dst, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch, (void*)&ld};
         drv.check(drv.launchKernel(st.fn, gridC, 1, 1, st.block, 1, 1, (unsigned)st.smem, (CUstream)stream, args, nullptr),
                   "cuLaunchKernel");
@@ -964,7 +999,8 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
     // The batch is first copied into a feature-major float matrix in scratch memory (one area per stream),
     // at most kLayeredChunk samples at a time; the layered kernels then read it coalesced.
     const size_t kLayeredChunk = st.layeredChunkRows;
-    float* xt = (float*)scratchFor(st, stream);
+    char* layeredScratch = (char*)scratchFor(st, stream);
+    float* xt = (float*)(layeredScratch + (st.useDual ? st.crossBytes : 0));
     const size_t rowBytes = (size_t)meta_.numFeatures * meta_.bytesPerFeature;
     for (size_t r0 = 0; r0 < n; r0 += kLayeredChunk) {
       const size_t rows = std::min(kLayeredChunk, n - r0);
@@ -980,6 +1016,7 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
       if (st.useDual) {
         DualArgs da = st.da;
         da.xtLd = (long long)ld;
+        da.globalStack = (float*)layeredScratch;
         CUDA_OK(layeredDualLaunch(da, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
       } else if (st.useTcf) CUDA_OK(layeredTcfLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, st.dStatus, stream));
       else if (st.useMma) CUDA_OK(layeredMmaLaunch(la, DT_F32, xt, dst, rows, gridC, st.smem, stream));

@@ -45,9 +45,12 @@ struct Options {
   int asyncStage = 1;          // "spnb-async-stage": 0 = never stage the next tile with cp.async while one is evaluated
   int scopeBytes = 0;          // "spnb-scope-bytes": staged bytes per sample and chunk (0 = what fits)
   int tcTiles = 2;             // "spnb-tc-tiles": 2 = two sample tiles per CTA where the model allows it, 1 = one tile
-  long long spinLimit = 0;     // "spnb-spin-limit": polls after which a tensor-core barrier wait gives up (0 = 2^22)
+  int tcRings = 0;             // "spnb-tc-rings": weight blocks and leaf stages in flight in the two-tile kernel (43, 42, 33, 32; 0 = deepest that fits)
+  int tcFoldScalar = 0;        // "spnb-tc-fold": packed (fma.rn.f32x2, default) or scalar FMAs in the two-tile kernel's fold
+  long long spinLimit = 0;     // "spnb-spin-limit": polls after which a tensor-core barrier wait gives up (0 = 2^17, about a second)
   int selftestWithhold = 0;    // "spnb-selftest-withhold-commit": 1 = the two-tile kernel leaves out one commit (tests
                                // that a bounded wait runs out and is reported; results of such a plan are invalid)
+  int bucketClamp = 0;         // "spnb-bucket-clamp": 1 = histogram buckets by multiply-shift-clamp where exact (no gain measured: off)
   int bucketArith = 0;         // "spnb-bucket-arith": 1 = compute histogram buckets by multiply-shift where exact (measured slower: off)
   int interpSlots = 0;         // "spnb-interp-slots": cap on the interpreter's shared-memory value slots (0 = as many as fit)
   int groupTiles = 0;          // "spnb-group-tiles": tiles per chunk run of a chunked kernel (0 = automatic)
@@ -100,8 +103,10 @@ class Engine {
   bool mmaSplit_ = true;
   int tcWarpgroups_ = 1;
   int tcTiles_ = 2;
-  unsigned spinLimit_ = 1u << 22;
+  unsigned spinLimit_ = 1u << 17;   // polls of mbarrier.try_wait, each of which may itself block for microseconds
   int selftestWithhold_ = 0;
+  int tcFoldScalar_ = 0;
+  int tcRings_ = 0;
   bool layeredTcf_ = false;
   std::string source_;
   std::vector<char> cubin_;

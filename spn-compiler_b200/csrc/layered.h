@@ -88,7 +88,7 @@ struct DualStepDev {
   int width;              // outputs
   int dest, destSlot;     // DualDest
   int aSrc;               // inner / root part: a-stack slot of the left operand, -1 = registers
-  int numBlocks;          // inner: blocks of 128 (k,i) columns; leaf: stages of four features (0: FP32 loop only)
+  int numBlocks;          // inner: blocks of 128 (k,i) columns; leaf: stages of eight features (0: FP32 loop only)
   long long fragOffset;   // byte offset of the step's weights in LayeredArgs::frags
   int scaleOffset;        // inner: first of 32 per-sum log2 scales
   int stageBase;          // leaf: first stage of the region in DualArgs::leafCols / leafCentres
@@ -99,12 +99,16 @@ struct DualStepDev {
 struct DualArgs {
   const DualStepDev* steps;
   int numSteps;
-  int aSlots;              // a-stack slots per tile
+  int aSlots;              // a-stack slots per tile in shared memory
+  int globalSlots;         // a-stack slots per tile kept in global memory instead (the outermost ones; slot ids below this)
+  float* globalStack;      // [grid][2][globalSlots][33][128] floats
   int ringBlocks;          // 16 KB weight blocks in flight (3 or 4)
+  int leafRing;            // leaf stages in flight (2 to 4)
   int marginal;
   const unsigned char* frags;   // same blocks as layeredTcfKernel reads
-  const float* scales;
-  const int* leafCols;          // per stage of four features (every region padded to a multiple of four stages):
+  const float* scales;          // per sum: base-2 log of the largest weight of its row (the one-tile kernel's form)
+  const float* scaleMul;        // per sum: that largest weight itself
+  const int* leafCols;          // per stage of eight features:
   const float* leafCentres;     //   input column (padding: 0) and the offset subtracted from the input
   int numLeafStages;
   const int* features;          // FP32 leaf path, as in LayeredArgs
@@ -112,9 +116,11 @@ struct DualArgs {
   long long xtLd;               // leading dimension of the feature-major input copy
   unsigned spinLimit;           // polls after which a barrier wait gives up
   int testWithholdCommit;       // self-test: the issuer leaves out one commit, so that a bounded wait runs out
+  int foldScalar;               // 1: the fold uses scalar FMAs instead of packed pairs (fma.rn.f32x2)
 };
 
-size_t layeredDualSmemBytes(int aSlots, int ringBlocks);
+size_t layeredDualSmemBytes(int aSlots, int ringBlocks, int leafRing);
+size_t layeredDualGlobalStackBytes(int grid, int globalSlots);
 
 }  // namespace spnb
 

@@ -327,12 +327,41 @@ Plan buildPlan(const Model& m, bool logSpace) {
               g.arMul = (int32_t)mul;
               g.arAdd = (int32_t)add;
             }
+          // the same search with the two staged special codes among the constraints
+          const int64_t oorCode = entries, nanCode = 65535;
+          for (int64_t dm = 0; dm <= 256 && !g.clampFit && oorCode < nanCode; ++dm)
+            for (int sgn = 0; sgn < (dm ? 2 : 1) && !g.clampFit; ++sgn) {
+              const int64_t mul = m0 + (sgn ? -dm : dm);
+              if (mul <= 0) continue;
+              int64_t lo = INT64_MIN, hi = INT64_MAX;
+              for (int64_t c = 2; c <= entries; ++c) {
+                const int64_t want = c < entries ? (int64_t)lut[(size_t)c] : (int64_t)g.count;
+                lo = std::max(lo, want * 65536 - c * mul);
+                hi = std::min(hi, (want + 1) * 65536 - 1 - c * mul);
+              }
+              lo = std::max(lo, ((int64_t)g.count + 1) * 65536 - nanCode * mul);   // missing input: at least count + 1
+              if (lo > hi) continue;
+              const int64_t add = lo + (hi - lo) / 2;
+              if (nanCode * mul + std::llabs(add) >= (int64_t)1 << 31 || 2 * mul + add < 0) continue;
+              g.clampFit = true;
+              g.clMul = (int32_t)mul;
+              g.clAdd = (int32_t)add;
+            }
         }
       }
       auto li = lutOf.emplace(lut, (int32_t)p.lut.size());
       if (li.second) p.lut.insert(p.lut.end(), lut.begin(), lut.end());
       g.lutOffset = li.first->second;
     }
+  }
+  // features all of whose discrete leaves can bucket arithmetically with clamped special codes
+  {
+    std::vector<int8_t> all(F, 1), any(F, 0);
+    for (const IndexGroup& g : p.groups) {
+      any[g.feature] = 1;
+      if (!(g.mode == kLut && g.clampFit)) all[g.feature] = 0;
+    }
+    for (int32_t f = 0; f < F; ++f) p.features[f].clampCodes = any[f] && all[f] && p.features[f].codeSlot >= 0;
   }
   // a feature whose code array is unused (all its groups generic) needs no code slot; harmless to keep
   for (size_t v = 0; v < n; ++v) {

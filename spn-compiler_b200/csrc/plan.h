@@ -40,6 +40,9 @@ struct FeatureMeta {
   int32_t domain = 0;
   int32_t codeSlot = -1;   // row of the staged code array, -1: no discrete leaf reads the feature
   int32_t valueSlot = -1;  // row of the staged value array, -1: no leaf needs the value itself
+  // every discrete leaf on the feature buckets its input arithmetically (IndexGroup::clampFit): a generated
+  // kernel may stage missing inputs as code 65535 and out-of-range ones as domain + 2 instead of 0 and 1
+  bool clampCodes = false;
 };
 
 // All discrete leaves on one feature that bucket the input the same way form a group.
@@ -60,6 +63,12 @@ struct IndexGroup {
   // code >= 2 (near-equal-width buckets): generated kernels may compute the bucket instead of loading it
   bool arith = false;
   int32_t arMul = 0, arAdd = 0;
+  // ... and a second fit that also sends the code one past the domain (domain + 2) to bucket `count`, the
+  // out-of-range entry, and the largest 16-bit code to at least count + 1: with the feature's missing inputs
+  // staged as 65535 and its out-of-range inputs as domain + 2 (FeatureMeta::clampCodes), the table index is
+  // min((code * clMul + clAdd) >> 16, count + 1) with no special cases and no byte table
+  bool clampFit = false;
+  int32_t clMul = 0, clAdd = 0;
 };
 
 struct PlanStats {

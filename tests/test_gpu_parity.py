@@ -275,6 +275,28 @@ def test_bounded_wait_runs_out_and_is_reported(capi, tmp_path):
     good.close()
 
 
+def test_histogram_buckets_by_arithmetic(capi, tmp_path):
+    """Equal-width histograms can bucket their input with multiply-shift instead of the byte table, either with
+    the standard special codes (spnb-bucket-arith) or with special codes staged so that one clamp does the rest
+    (spnb-bucket-clamp); both must agree with the byte-table path and the oracle, NaN and out-of-range inputs
+    included."""
+    name, spn, inputs, log_space, marginal = small_configs()[3]
+    q = write_query(spn, marginal, directory=str(tmp_path))
+    x = inputs(50001)
+    x[::13, 7] = 300.0      # outside every histogram
+    x[::17, 9] = -5.0
+    want = oracle_eval(q, x, True)
+    for extra in (dict(spnb_bucket_clamp=1), dict(spnb_bucket_arith=1), dict(spnb_bucket_clamp=1, spnb_scoped=1, spnb_chunk_nodes=200)):
+        plan_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="unrolled", **extra))
+        plan = capi.Plan(plan_path)
+        if "spnb_bucket_clamp" in extra:
+            assert "min((" in plan.source
+        err = max_rel_err(plan.execute_host(x), want)
+        assert err <= REL_TOL_F32, (extra, err)
+        plan.close()
+        os.remove(plan_path)
+
+
 def test_streamed_table_window(capi, tmp_path):
     """Leaf tables larger than the shared-memory window are reloaded piecewise inside the kernel body."""
     for idx in (3, 4, 1):
