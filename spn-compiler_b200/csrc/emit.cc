@@ -169,8 +169,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     if (opt.scopeBytes > 0) scopeBudget = std::min<size_t>(scopeBudget, (size_t)opt.scopeBytes);
     // Values alive across position q (defined before q, used at or after q): what a cut at q sends through
     // the scratch area.  A chunk is grown until its leaves would need more staged bytes than fit (or it has
-    // chunkNodes nodes); the cut is then placed at the position of its second half where the fewest values
-    // cross, which is where one sub-DAG ends and the next begins in the depth-first evaluation order.
+    // chunkNodes nodes); with scopeCut = 1 the cut is then moved back to the position of its second half where
+    // the fewest values cross, which is where one sub-DAG ends and the next begins in the depth-first order.
     std::vector<int32_t> crossing(n + 1, 0);
     {
       std::vector<int64_t> last(n, -1);
@@ -210,7 +210,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
         bytes += add;
       }
       size_t cut = reach;
-      if (reach < n) {
+      if (reach < n && opt.scopeCut == 1) {
         const size_t lo = begin + std::max<size_t>(1, (reach - begin) / 2);
         for (size_t q = lo; q <= reach; ++q)
           if (crossing[q] <= crossing[cut]) cut = q;
@@ -471,7 +471,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
         const int32_t c = d.childIdx[e];
         if ((size_t)c < v0 && !loaded[c]) { loaded[c] = 1; incoming.push_back(c); }
       }
-    if (incoming.size() <= 24) {
+    if (incoming.size() <= (size_t)std::max(opt.hoistLoads, 0)) {
       for (int32_t c : incoming)
         o << "  real_t " << V(c) << "; asm volatile(\"" << ldGlobal << " %0, [%1+" << (long long)crossSlot[c] * TILE * rb
           << "];\" : \"=" << cReal << "\"(" << V(c) << ") : \"l\"(sc) : \"memory\");\n";

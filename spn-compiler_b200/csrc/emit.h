@@ -33,6 +33,11 @@ struct EmitOptions {
   // CTA of 1024 samples impossible otherwise), 0 = never, 1 = whenever the inputs are float32 in log space.
   int scoped = -1;
   int scopeBytes = 0;              // staged bytes per sample and chunk (0 = what fits beside the table window)
+  // Where a scope-local chunk ends once its staging budget is used up: 0 = right there; 1 = at the position of its
+  // second half where the fewest values are alive (fewer values through scratch, but a third more chunks and
+  // with them more re-staged features: measured 89-92 ms against 86.8 ms on the 53 k-node model, so 0 is the default).
+  int scopeCut = 0;
+  int hoistLoads = 0;              // scope-local chunks request up to this many operands of earlier chunks at their top
   // Asynchronous double-buffered staging (float32 inputs that are all read as values, log space): tile t + 1 is
   // copied global -> shared with cp.async while tile t is evaluated.  Rows keep their order with an odd stride,
   // so neither the copy nor the body's reads conflict on shared-memory banks and nothing is transposed.

@@ -226,6 +226,8 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-scoped") o.scoped = std::atoi(v.c_str());
     else if (k == "spnb-async-stage") o.asyncStage = std::atoi(v.c_str());
     else if (k == "spnb-scope-bytes") o.scopeBytes = std::atoi(v.c_str());
+    else if (k == "spnb-scope-cut") o.scopeCut = std::atoi(v.c_str());
+    else if (k == "spnb-hoist-loads") o.hoistLoads = std::atoi(v.c_str());
     else if (k == "spnb-tc-tiles") {
       o.tcTiles = std::atoi(v.c_str());
       if (o.tcTiles != 1 && o.tcTiles != 2) fail("spnb-tc-tiles must be 1 or 2");
@@ -299,6 +301,8 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     eo.scoped = opt.scoped;
     eo.asyncStage = opt.asyncStage;
     eo.scopeBytes = opt.scopeBytes;
+    eo.scopeCut = opt.scopeCut;
+    eo.hoistLoads = opt.hoistLoads;
     source = emitCuda(plan, eo, &ei);
     if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
     jr = jitCompile(source, m.name, opt.optLevel, opt.maxRegisters);

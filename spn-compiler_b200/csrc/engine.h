@@ -43,6 +43,8 @@ struct Options {
   int tcWarpgroups = 1;        // "spnb-tc-warpgroups": warpgroups (128 threads) per CTA of the tensor-memory layered kernel
   int scoped = -1;             // "spnb-scoped": scope-local staging of a chunked generated kernel (-1 automatic, 0 off, 1 on)
   int asyncStage = 1;          // "spnb-async-stage": 0 = never stage the next tile with cp.async while one is evaluated
+  int scopeCut = 0;            // "spnb-scope-cut": 1 = end scope-local chunks where the fewest values are alive
+  int hoistLoads = 0;          // "spnb-hoist-loads": operands of earlier chunks a scope-local chunk requests at its top
   int scopeBytes = 0;          // "spnb-scope-bytes": staged bytes per sample and chunk (0 = what fits)
   int tcTiles = 2;             // "spnb-tc-tiles": 2 = two sample tiles per CTA where the model allows it, 1 = one tile
   int tcRings = 0;             // "spnb-tc-rings": weight blocks and leaf stages in flight in the two-tile kernel (43, 42, 33, 32; 0 = deepest that fits)

@@ -779,6 +779,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
                                                  xpair + (size_t)__ldg(a.leafCols + g * STAGE_FEATS + (int)lane - 1) * a.xtLd,
                                                  NTILE * TS * 4, full);
           else if (lane == STAGE_FEATS + 1) bulkLoad(dst + LW_STAGE + LEAF_X, a.leafCentres + (size_t)g * STAGE_FEATS, STAGE_FEATS * 4, full);
+          // (Asking rows of later stages into L2 ahead of time with cp.async.bulk.prefetch.L2 made the 2 M-sample
+          // step slower, 221 ms against 201 ms: the tile pairs of all CTAs together are about as large as L2.)
           __syncwarp();
           ++issued;
         }

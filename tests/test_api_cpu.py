@@ -236,3 +236,18 @@ def test_two_tile_tensor_core_program(tmp_path):
     path, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "layered", "spnb-tc-tiles": "1"})
     with pytest.raises(capi.SpnbError, match="spnb-tc-tiles"):
         capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-tc-tiles": "3"})
+
+
+def test_bench_batch_is_the_same_for_every_gpu_count():
+    """bench.py cuts ONE batch into one shard per rank (strong scaling): the shards of 2, 4 and 8 ranks put
+    together are the batch a single rank evaluates."""
+    import bench
+    from spnb import synth
+    spn = synth.config2(target_nodes=300)
+    n = 8 * 1000 + 8
+    whole = bench.shard_inputs(2, spn, n, 1, 0)
+    assert whole.shape == (n, 26)
+    for world in (2, 4, 8):
+        parts = [bench.shard_inputs(2, spn, n, world, r) for r in range(world)]
+        assert np.array_equal(np.concatenate(parts), whole)
+        assert sum(len(p) for p in parts) == n

@@ -111,8 +111,12 @@ def test_scope_local_staging(capi, tmp_path):
     name, spn, inputs, log_space, marginal = small_configs()[4]
     q = write_query(spn, marginal, directory=str(tmp_path))
     for budget, chunk in ((0, 2000), (64, 300), (16, 97)):
+        # the middle variant also ends its chunks where the fewest values are alive and requests the operands
+        # of earlier chunks at the top of each function
         plan_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="unrolled", spnb_scoped=1, spnb_scope_bytes=budget,
-                                                   spnb_chunk_nodes=chunk, spnb_table_window=4096))
+                                                   spnb_chunk_nodes=chunk, spnb_table_window=4096,
+                                                   spnb_scope_cut=1 if budget == 64 else 0,
+                                                   spnb_hoist_loads=24 if budget == 64 else 0))
         plan = capi.Plan(plan_path)
         st = plan.stats
         assert st["scoped_staging"] and st["tile"] == 1024 and st["chunks"] > 1
