@@ -497,6 +497,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # NCCL writes its version banner (NCCL_DEBUG=VERSION and above) to stdout: stdout carries the JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cfg = CONFIGS[args.config]
     n_total = args.samples or cfg["n"]
