@@ -68,8 +68,76 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const bool lg = p.logSpace;
   const char* real = lg ? "float" : "double";
   const int F = d.numFeatures;
-  const size_t tabEntries = lg ? p.tabF32.size() : p.tabF64.size();
+  size_t tabEntries = lg ? p.tabF32.size() : p.tabF64.size();
   const size_t realBytes = lg ? 4 : 8;
+  // ---- fused leaf tables ---------------------------------------------------------------------------------
+  // A product's discrete leaf children over distinct features, each read through a (domain + 2)-entry table,
+  // are looked up together: one table over the combined code  c1 + S1 * (c2 + S2 * c3)  holds the product of
+  // the leaves' values (the sum of their logarithms), so k leaves cost one table read and k - 1 integer
+  // multiply-adds instead of k reads and k - 1 floating-point operations.  Small discrete models are bound by
+  // the shared-memory pipe (two wavefronts per 64-bit table read), not by arithmetic.  Only for kernels of one
+  // function whose tables, the fused ones included, stay resident in shared memory; a leaf with another
+  // consumer keeps its own read.  The fused tables follow the plan's tables in the table image.
+  struct FusedGroup { std::vector<int32_t> leaves; long long offset = 0; };
+  std::vector<FusedGroup> fused;
+  std::vector<int32_t> fusedHead(n, -1);     // leaf -> its group, for the group's first leaf in evaluation order
+  std::vector<uint8_t> fusedAway(n, 0);      // leaf evaluated by its group's first leaf
+  std::vector<double> fusedTable;
+  {
+    const size_t cn = opt.chunkNodes > 0 ? (size_t)opt.chunkNodes : n;
+    const bool oneFunction = opt.chunkExact ? n <= cn : n <= cn + cn / 2;
+    const size_t cap = (size_t)opt.smemTableLimit / realBytes;
+    if (opt.fuseLeaves != 0 && oneFunction && opt.scoped != 1 && !opt.bucketClamp && tabEntries > 0 && tabEntries < cap) {
+      std::vector<int32_t> uses(n, 0);
+      for (size_t v = 0; v < n; ++v)
+        for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) ++uses[d.childIdx[e]];
+      auto entriesOf = [&](int32_t c) -> long long {
+        if (d.kind[c] != kCategorical && d.kind[c] != kHistogram) return 0;
+        const IndexGroup& G = p.groups[d.group[c]];
+        if (G.mode != kDirect || uses[c] != 1 || p.tabOffset[c] < 0) return 0;
+        return (long long)p.features[G.feature].domain + 2;
+      };
+      const long long maxEntries = std::max(opt.fuseEntries, 4);
+      for (size_t v = 0; v < n; ++v) {
+        if (d.kind[v] != kProduct) continue;
+        FusedGroup g;
+        long long size = 1;
+        auto close = [&]() {
+          if (g.leaves.size() >= 2 && tabEntries + fusedTable.size() + (size_t)size <= cap) {
+            g.offset = (long long)(tabEntries + fusedTable.size());
+            // entry of the combined code: leaf 0's code runs fastest
+            for (long long idx = 0; idx < size; ++idx) {
+              long long rest = idx;
+              double acc = lg ? 0.0 : 1.0;
+              for (int32_t c : g.leaves) {
+                const long long sz = entriesOf(c), code = rest % sz;
+                rest /= sz;
+                const double t = lg ? (double)p.tabF32[(size_t)p.tabOffset[c] + (size_t)code] : p.tabF64[(size_t)p.tabOffset[c] + (size_t)code];
+                acc = lg ? acc + t : acc * t;
+              }
+              fusedTable.push_back(acc);
+            }
+            int32_t head = *std::min_element(g.leaves.begin(), g.leaves.end());
+            fusedHead[head] = (int32_t)fused.size();
+            for (int32_t c : g.leaves) if (c != head) fusedAway[c] = 1;
+            fused.push_back(g);
+          }
+          g.leaves.clear();
+          size = 1;
+        };
+        for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
+          const int32_t c = d.childIdx[e];
+          const long long sz = entriesOf(c);
+          if (sz == 0) continue;
+          if (size * sz > maxEntries) close();
+          g.leaves.push_back(c);
+          size *= sz;
+        }
+        close();
+      }
+      tabEntries += fusedTable.size();
+    }
+  }
   // Launch shape.  The body is far larger than the instruction caches, so the warps of an SM should
   // walk it together: few, large CTAs (their warps leave the staging barrier at the same time), and
   // 1024 resident threads per SM at <= 64 registers when the staged inputs of that many samples fit
@@ -134,6 +202,12 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // table lies beyond the window the CTA reloads the window from global memory between two barriers.
   const bool tabSmem = tabEntries > 0;
   const bool streamed = tabBytes > tableLimit;
+  if (streamed && !fused.empty()) {
+    // the fused tables do not follow the leaves' order, which a streamed window relies on: emit without them
+    EmitOptions plain = opt;
+    plain.fuseLeaves = 0;
+    return emitCuda(p, plain, info);
+  }
   const size_t winBytes = streamed ? (tableLimit & ~size_t(15)) : ((tabBytes + 15) & ~size_t(15));
   const bool floatIn = p.ftype.isFloat();
   const double LOG2E = 1.4426950408889634074;
@@ -159,13 +233,14 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // per chunk: staged features (values, then codes) and, per node, the slot its leaf reads
   std::vector<std::vector<int32_t>> chunkValueFeat, chunkCodeFeat;
   std::vector<int32_t> leafSlot(n, -1);
-  size_t scopeBudget = 0, maxStageBytes = 0;
+  size_t scopeBudget = 0, maxStageBytes = 0, maxValueFeat = 0, maxCodeFeat = 0;
+  bool fixedCodeBase = false;
   if (!scoped) {
     for (size_t v = chunkNodes; v < n; v += chunkNodes) chunkStart.push_back(v);
     for (size_t v = 0; v < n; ++v) chunkOf[v] = (int32_t)(v / chunkNodes);
   } else {
     const size_t fixed = 64 + std::min(tabBytes, tableLimit) + 16 + (lutSmem ? p.lut.size() + 4 : 0);
-    scopeBudget = (226 * 1024 - fixed) / (size_t)TILE - (nanFlagsWanted ? 4 : 0);
+    scopeBudget = (226 * 1024 - fixed) / (size_t)TILE - (nanFlagsWanted ? 4 : 0) - (size_t)std::max(opt.prefetchSlots, 0) * 4;
     if (opt.scopeBytes > 0) scopeBudget = std::min<size_t>(scopeBudget, (size_t)opt.scopeBytes);
     // Values alive across position q (defined before q, used at or after q): what a cut at q sends through
     // the scratch area.  A chunk is grown until its leaves would need more staged bytes than fit (or it has
@@ -190,6 +265,20 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
         if (G.mode == kGeneric) needValue = G.feature; else needCode = G.feature;
       }
     };
+    // Without CTA-wide barriers between the chunks (chunkBarrier = 0) a warp may stage its next chunk while
+    // another still evaluates the current one.  A thread's staged words and bytes must then never share an address
+    // with another thread's, whatever the two chunks stage: values (words) and codes (bytes / half-words) get
+    // separate areas with one boundary for all chunks, and separate budgets in proportion to the model's features.
+    size_t valueBudget = scopeBudget, codeBudget = scopeBudget;
+    const bool splitAreas = opt.chunkBarrier == 0;
+    if (splitAreas) {
+      size_t fv = 0, fc = 0;
+      for (int f = 0; f < F; ++f) { fv += p.features[f].valueSlot >= 0; fc += p.features[f].codeSlot >= 0; }
+      if (fv && fc) {
+        valueBudget = std::max<size_t>(4, scopeBudget * (4 * fv) / (4 * fv + (size_t)cb * fc) / 4 * 4);
+        codeBudget = std::max<size_t>((size_t)cb, scopeBudget - valueBudget);
+      }
+    }
     std::vector<int32_t> vstamp(F, -1), cstamp(F, -1), vslotOf(F, -1), cslotOf(F, -1);
     chunkStart.clear();
     int32_t cur = 0, stamp = 0;
@@ -197,17 +286,20 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     while (begin < n) {
       // how far the budget reaches
       ++stamp;
-      size_t bytes = 0, reach = begin;
+      size_t bytes = 0, vbytes = 0, cbytes = 0, reach = begin;
       for (; reach < n && reach - begin < chunkNodes; ++reach) {
         int32_t nv, nc;
         needOf(reach, nv, nc);
-        size_t add = 0;
-        if (nv >= 0 && vstamp[nv] != stamp) add = 4;
-        if (nc >= 0 && cstamp[nc] != stamp) add = (size_t)cb;
-        if (bytes + add > scopeBudget && reach > begin) break;
+        size_t addV = 0, addC = 0;
+        if (nv >= 0 && vstamp[nv] != stamp) addV = 4;
+        if (nc >= 0 && cstamp[nc] != stamp) addC = (size_t)cb;
+        if (reach > begin && (bytes + addV + addC > scopeBudget ||
+                              (splitAreas && (vbytes + addV > valueBudget || cbytes + addC > codeBudget)))) break;
         if (nv >= 0) vstamp[nv] = stamp;
         if (nc >= 0) cstamp[nc] = stamp;
-        bytes += add;
+        bytes += addV + addC;
+        vbytes += addV;
+        cbytes += addC;
       }
       size_t cut = reach;
       if (reach < n && opt.scopeCut == 1) {
@@ -244,13 +336,17 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       ++cur;
       begin = cut;
     }
-    for (size_t c = 0; c < chunkValueFeat.size(); ++c)
+    for (size_t c = 0; c < chunkValueFeat.size(); ++c) {
       maxStageBytes = std::max(maxStageBytes, chunkValueFeat[c].size() * 4 + chunkCodeFeat[c].size() * (size_t)cb);
+      maxValueFeat = std::max(maxValueFeat, chunkValueFeat[c].size());
+      maxCodeFeat = std::max(maxCodeFeat, chunkCodeFeat[c].size());
+    }
+    if (splitAreas) { fixedCodeBase = true; maxStageBytes = maxValueFeat * 4 + maxCodeFeat * (size_t)cb; }
   }
   chunkStart.push_back(n);
   const size_t nChunks = chunkStart.size() - 1;
   // byte offset of a chunk's staged codes behind its staged values (scoped path)
-  auto codeBase = [&](size_t c) { return chunkValueFeat[c].size() * (size_t)4 * SX; };
+  auto codeBase = [&](size_t c) { return (fixedCodeBase ? maxValueFeat : chunkValueFeat[c].size()) * (size_t)4 * SX; };
   // Gaussian leaves of a query with marginal support must turn a NaN input into log 1 = 0: a compare
   // and a select per leaf.  NaNs are rare in practice, so the body is emitted twice: a plain version
   // and a NaN-aware one; a CTA takes the second only if one of its samples has a NaN among the staged
@@ -265,7 +361,11 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
                         : scoped ? ((maxStageBytes * SX + 15) & ~size_t(15)) : ((offCs + (size_t)NC * SX * cb + 15) & ~size_t(15));
   const size_t offLut = offTab + (tabSmem ? winBytes : 0);
   const size_t offNan = (offLut + (lutSmem ? p.lut.size() : 0) + 3) & ~size_t(3);
-  const size_t smemTotal = offNan + ((twoBodies && !scoped && !asyncStage) ? (size_t)TILE * 4 : 0);
+  // scope-local staging with an operand ring: [slot][TILE] floats behind everything else
+  const int pfSlots = scoped && lg ? std::max(opt.prefetchSlots, 0) : 0;
+  const size_t offPf = (offNan + 15) & ~size_t(15);
+  const size_t smemTotal = pfSlots > 0 ? offPf + (size_t)pfSlots * TILE * 4
+                                       : offNan + ((twoBodies && !scoped && !asyncStage) ? (size_t)TILE * 4 : 0);
 
   std::ostringstream o;
   o << "// generated by spnb: straight-line joint log-likelihood kernel, one thread per sample\n";
@@ -449,6 +549,19 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   // ---- the DAG body: its own non-inlined function (the asm reads above must not move across the
   // barrier that follows the staging of a tile) ------------------------------------------------------
   std::vector<long long> winEnd(nChunks, 0);
+  // operand ring (see emitBody): per chunk the operands it takes from earlier chunks, in the order of their first use
+  std::vector<std::vector<int32_t>> ringOrderOf(pfSlots > 0 && nChunks > 1 ? nChunks : 0);
+  for (size_t c = 0; c < ringOrderOf.size(); ++c) {
+    std::vector<uint8_t> seen(n, 0);
+    for (size_t v = chunkStart[c]; v < chunkStart[c + 1]; ++v)
+      for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
+        const int32_t ch = d.childIdx[e];
+        if ((size_t)ch < chunkStart[c] && !seen[ch]) { seen[ch] = 1; ringOrderOf[c].push_back(ch); }
+      }
+  }
+  // the first copies of a chunk are issued at the end of the chunk before it (they then overlap the staging of the
+  // chunk's inputs), unless a chunk runs on several tiles in a row
+  const bool ringAcross = groupTiles == 1;
   auto emitBody = [&](const std::string& fname, bool nanAware, size_t chunk) {
   const size_t v0 = chunkStart[chunk], v1 = chunkStart[chunk + 1];
   o << "static __device__ __noinline__ out_t " << fname << "(const unsigned xs_s, const unsigned cs_s, const unsigned tab_s, "
@@ -479,16 +592,69 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       for (int32_t c : incoming) loaded[c] = 0;
     }
   }
+  // Operands defined by an earlier chunk are fetched from the scratch area `loadAhead` nodes before the node
+  // that uses them first (0: at the first use): the request is then in flight while the nodes in between are
+  // evaluated, at the price of one register per outstanding value.  Moving such a load up crosses no store to
+  // its slot: a slot is released only after its value's last consumer, and that consumer is not before the
+  // node the load was moved up from, so no node in between can have been given the slot.
+  // Operand ring (scope-local staging, prefetchSlots > 0): the operands a chunk takes from earlier chunks are
+  // copied scratch -> shared memory with cp.async, in the order of their first use, `prefetchSlots` of them ahead
+  // of the evaluation; a use waits for its own copy group (the groups complete in order), reads its slot and
+  // hands the slot to the next copy.  Thread = sample on both sides, so no barrier is involved, the copies hold
+  // no registers, and the assembler cannot move them back down to the uses.
+  std::vector<int32_t> ringIndex(pfSlots > 0 && nChunks > 1 ? n : 0, -1);   // per incoming operand: its place in the order
+  const std::vector<int32_t> noOrder;
+  const std::vector<int32_t>& ringOrder = ringIndex.empty() ? noOrder : ringOrderOf[chunk];
+  size_t ringIssued = 0;
+  auto ringCopy = [&](const std::vector<int32_t>& order, size_t k) {
+    o << "  asm volatile(\"cp.async.ca.shared.global [%0+" << (k % (size_t)pfSlots) * TILE * 4 << "], [%1+"
+      << (long long)crossSlot[order[k]] * TILE * rb << "], 4; cp.async.commit_group;\" :: \"r\"(pf_t), \"l\"(sc) : \"memory\");\n";
+  };
+  if (!ringIndex.empty()) {
+    for (size_t k = 0; k < ringOrder.size(); ++k) ringIndex[ringOrder[k]] = (int32_t)k;
+    o << "  const unsigned pf_t = xs_s + " << offPf << "u + 4u * tid;\n";
+    const size_t first = std::min(ringOrder.size(), (size_t)pfSlots);
+    if (ringAcross && chunk > 0) ringIssued = first;   // in flight since the end of the chunk before
+    else while (ringIssued < first) ringCopy(ringOrder, ringIssued++);
+  }
+  const size_t loadAhead = nChunks > 1 && ringIndex.empty() ? (size_t)std::max(opt.loadAhead, 0) : 0;
+  // loadMode 1: the early request is a prefetch into L1 (no register is held), the load stays at the first use;
+  // loadMode 2: the early load is a volatile one, which the assembler does not move back down to its use
+  const int loadMode = opt.loadMode;
+  const char* ldEarly = loadMode == 2 ? (lg ? "ld.volatile.global.f32" : "ld.volatile.global.f64") : ldGlobal;
+  std::vector<uint8_t> requested(nChunks > 1 ? n : 0, 0);
+  size_t aheadDone = v0;   // nodes [v0, aheadDone) have had their operands requested
+  auto emitLoad = [&](int32_t c, const char* op) {
+    loaded[c] = 1;
+    o << "  real_t " << V(c) << "; asm volatile(\"" << op << " %0, [%1+" << (long long)crossSlot[c] * TILE * rb
+      << "];\" : \"=" << cReal << "\"(" << V(c) << ") : \"l\"(sc) : \"memory\");\n";
+  };
   for (size_t v = v0; v < v1; ++v) {
-    // operands defined by an earlier chunk are fetched from the scratch area on first use
-    if (nChunks > 1)
+    if (nChunks > 1) {
+      const size_t upTo = std::min(v1, v + loadAhead + 1);
+      for (size_t u = std::max(aheadDone, v); u < upTo && ringIndex.empty(); ++u)
+        for (int64_t e = d.childPtr[u]; e < d.childPtr[u + 1]; ++e) {
+          const int32_t c = d.childIdx[e];
+          if ((size_t)c >= v0 || loaded[c] || requested[c]) continue;
+          requested[c] = 1;
+          if (loadMode == 1 && u > v)
+            o << "  asm volatile(\"prefetch.global.L1 [%0+" << (long long)crossSlot[c] * TILE * rb << "];\" :: \"l\"(sc) : \"memory\");\n";
+          else
+            emitLoad(c, u > v ? ldEarly : ldGlobal);
+        }
+      aheadDone = std::max(aheadDone, upTo);
       for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
         const int32_t c = d.childIdx[e];
         if ((size_t)c >= v0 || loaded[c]) continue;
+        if (ringIndex.empty()) { emitLoad(c, ldGlobal); continue; }
+        // groups newer than this operand's may still be pending
+        const size_t k = (size_t)ringIndex[c];
         loaded[c] = 1;
-        o << "  real_t " << V(c) << "; asm volatile(\"" << ldGlobal << " %0, [%1+" << (long long)crossSlot[c] * TILE * rb
-          << "];\" : \"=" << cReal << "\"(" << V(c) << ") : \"l\"(sc) : \"memory\");\n";
+        o << "  real_t " << V(c) << "; asm volatile(\"cp.async.wait_group " << (ringIssued - 1 - k) << "; ld.shared.f32 %0, [%1+"
+          << (k % (size_t)pfSlots) * TILE * 4 << "];\" : \"=f\"(" << V(c) << ") : \"r\"(pf_t) : \"memory\");\n";
+        if (ringIssued < ringOrder.size()) ringCopy(ringOrder, ringIssued++);
       }
+    }
     if (opt.syncEvery > 0 && v > 0 && v % (size_t)opt.syncEvery == 0) o << "  __syncthreads();\n";
     const std::string name = V((int32_t)v);
     int64_t lo = d.childPtr[v], hi = d.childPtr[v + 1];
@@ -521,12 +687,29 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       }
       case kCategorical:
       case kHistogram:
+        if (fusedAway[v]) break;   // read by its group's first leaf
+        if (fusedHead[v] >= 0) {
+          // combined code of the group's leaves, then one read of the fused table
+          const FusedGroup& g = fused[(size_t)fusedHead[v]];
+          std::string idx;
+          for (size_t q = g.leaves.size(); q-- > 0;) {
+            const int32_t c = g.leaves[q];
+            const FeatureMeta& fm = p.features[p.groups[d.group[c]].feature];
+            const std::string cn = "c" + std::to_string(c);
+            o << readCode(cn, fm.codeSlot, (long long)c);
+            idx = idx.empty() ? cn : "(" + cn + " + " + std::to_string(fm.domain + 2) + " * " + idx + ")";
+          }
+          o << "  const int fi" << v << " = " << idx << ";\n";
+          o << readTab(name, g.offset, "fi" + std::to_string(v), (long long)v);
+          break;
+        }
         if (streamed && (p.tabOffset[v] + tableEntriesOf(v) - winBase) * rb > (long long)winBytes) swapWindow(o, p.tabOffset[v]);
         emitLeafLookup(o, v, name);
         break;
       case kProduct: {
         terms.clear();
-        for (int64_t e = lo; e < hi; ++e) terms.push_back(V(d.childIdx[e]));
+        for (int64_t e = lo; e < hi; ++e)
+          if (!fusedAway[d.childIdx[e]]) terms.push_back(V(d.childIdx[e]));
         const char* op = lg ? " + " : " * ";
         o << "  const real_t " << name << " = "
           << balanced(terms, 0, terms.size(), [&](const std::string& a, const std::string& b) { return "(" + a + op + b + ")"; }) << ";\n";
@@ -571,6 +754,10 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       o << "  asm volatile(\"" << stGlobal << " [%0+" << (long long)crossSlot[v] * TILE * rb << "], %1;\" :: \"l\"(sc), \""
         << cReal << "\"(" << name << ") : \"memory\");\n";
   }
+  if (!ringIndex.empty() && ringAcross && chunk + 1 < nChunks) {
+    const std::vector<int32_t>& next = ringOrderOf[chunk + 1];
+    for (size_t k = 0; k < next.size() && k < (size_t)pfSlots; ++k) ringCopy(next, k);
+  }
   if (v1 < n) o << "  return (out_t)0;\n}\n";
   else if (lg) o << "  return " << V(d.root()) << " * 0x1.62e43p-1f;\n}\n";  // log2 -> ln
   else o << "  return log(" << V(d.root()) << ");\n}\n";
@@ -609,10 +796,10 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "static __device__ __noinline__ int spnb_stage(unsigned char* __restrict__ smem, const float* __restrict__ src, const unsigned long long ld,\n"
          "                                              const int* __restrict__ cf, const int nv, const int nc, const unsigned codeBase, const unsigned tid)\n{\n";
     o << "  float* xs = reinterpret_cast<float*>(smem);\n  code_t* cs = reinterpret_cast<code_t*>(smem + codeBase);\n  int nan = 0;\n";
-    o << "#pragma unroll 8\n";
+    o << "#pragma unroll " << std::max(opt.stageUnroll, 1) << "\n";
     o << "  for (int j = 0; j < nv; ++j) { const float raw = src[(unsigned long long)__ldg(cf + j) * ld]; xs[j * SX + tid] = raw; nan |= (raw != raw); }\n";
     o << "  cf += nv;\n";
-    o << "#pragma unroll 8\n";
+    o << "#pragma unroll " << std::max(opt.stageUnroll, 1) << "\n";
     o << "  for (int j = 0; j < nc; ++j) {\n";
     o << "    const float raw = src[(unsigned long long)__ldg(cf + 3 * j) * ld];\n";
     o << "    const unsigned rr = (unsigned)TOINT(raw) - (unsigned)__ldg(cf + 3 * j + 1);\n";
@@ -640,6 +827,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       o << "  { unsigned char* lut = smem_raw + " << offLut << ";\n";
       o << "    for (unsigned i = tid; i < NLUT; i += TILE) lut[i] = lut_g[i];\n    lut_s = (unsigned)__cvta_generic_to_shared(lut); }\n";
     }
+    if ((tabSmem && !streamed) || lutSmem) o << "  __syncthreads();   // tables loaded above are read by every thread\n";
     o << "  const unsigned long long ntiles = (n + TILE - 1) / TILE;\n";
     // Every chunk runs on groupTiles tiles in a row (each with its own slice of the cross-chunk scratch), so
     // that its code, which fits the instruction cache, is fetched once per group instead of once per tile.
@@ -661,7 +849,14 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       o << "      // threads past the end of the batch repeat its last sample; their result is not stored\n";
       o << "      const float* __restrict__ src = xt + base + (tid < rows ? tid : rows - 1);\n";
       o << "      real_t* sct = sc + (size_t)t * " << nCross << "u * TILE;\n";
-      o << "      __syncthreads();\n";
+      // Thread = sample on both sides of the staging area: a thread stages and reads its own column only, so
+      // the chunks need no CTA-wide barrier between them.  Without one the warps drift apart and one warp's
+      // staging loads overlap the other warps' arithmetic; the plain / NaN-aware choice is then made per warp.
+      // (The barriers around a swap of the table window stay: every warp passes the same swaps in the same
+      // order, whichever variants it takes.)
+      const bool barrier = opt.chunkBarrier != 0;
+      const std::string anyNan = barrier ? "__syncthreads_or(nan)" : "__any_sync(0xffffffffu, nan)";
+      if (barrier) o << "      __syncthreads();\n";
       const bool choose = twoBodies && nv > 0;
       o << "      " << (choose ? "const int nan = " : "") << "spnb_stage(smem_raw, src, ld, CF + " << cfOff[c] << ", " << nv << ", " << nc << ", "
         << codeBase(c) << "u, tid);\n";
@@ -671,14 +866,14 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       if (choose) {
         if (last) {
           o << "      out_t res;\n";
-          o << "      if (__syncthreads_or(nan)) res = spnb_body_nan" << c << args;
+          o << "      if (" << anyNan << ") res = spnb_body_nan" << c << args;
           o << "      else res = spnb_body" << c << args;
         } else {
-          o << "      if (__syncthreads_or(nan)) spnb_body_nan" << c << args;
+          o << "      if (" << anyNan << ") spnb_body_nan" << c << args;
           o << "      else spnb_body" << c << args;
         }
       } else {
-        o << "      __syncthreads();\n";
+        if (barrier) o << "      __syncthreads();\n";
         o << "      " << lhs << "spnb_body" << c << args;
       }
       if (last) o << "      if (tid < rows) out[base + tid] = res;\n";
@@ -691,6 +886,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       info->inputStride = SX;
       info->tablesInSmem = tabSmem;
       info->tableEntries = tabEntries;
+      info->fusedTable = fusedTable;
+      info->fusedGroups = (int)fused.size();
       info->dynamicSmemBytes = smemTotal;
       info->scratchSlots = nCross * groupTiles;
       info->scoped = true;
@@ -762,6 +959,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       info->inputStride = RS;
       info->tablesInSmem = tabSmem;
       info->tableEntries = tabEntries;
+      info->fusedTable = fusedTable;
+      info->fusedGroups = (int)fused.size();
       info->dynamicSmemBytes = smemTotal;
       info->scratchSlots = nCross;
       info->scoped = false;
@@ -806,11 +1005,11 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << ind << "  const in_t* __restrict__ src = in + base * NF;\n";
     o << ind << "  const unsigned total = rows * NF;\n";
     if (identity) {
-      o << "#pragma unroll 4\n";
+      o << "#pragma unroll " << std::max(opt.rowStageUnroll, 1) << "\n";
       o << ind << "  for (unsigned e = tid; e < total; e += TILE) { const unsigned r = e / NF; const unsigned c = e - r * NF; const in_t raw = src[e]; xs[c * SX + r] = (real_t)raw;" << (twoBodies ? " if (raw != raw) nanrow[r] = 1;" : "") << " }\n";
       o << ind << "  if (rows < TILE) for (unsigned e = total + tid; e < TILE * NF; e += TILE) { const unsigned r = e / NF; const unsigned c = e - r * NF; xs[c * SX + r] = (real_t)0; }\n";
     } else {
-      o << "#pragma unroll 4\n";
+      o << "#pragma unroll " << std::max(opt.rowStageUnroll, 1) << "\n";
       o << ind << "  for (unsigned e = tid; e < TILE * NF; e += TILE) {\n";
       o << ind << "    const unsigned r = e / NF; const unsigned c = e - r * NF;\n";
       o << ind << "    const int4 m = fm[c];\n";
@@ -892,6 +1091,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     info->inputStride = SX;
     info->tablesInSmem = tabSmem;
     info->tableEntries = tabEntries;
+      info->fusedTable = fusedTable;
+      info->fusedGroups = (int)fused.size();
     info->dynamicSmemBytes = smemTotal;
     info->scratchSlots = nCross * std::max(groupTiles, 1);
     info->scoped = false;

@@ -3,6 +3,7 @@
 // (mlir/lib/Conversion/LoSPNtoGPU/GPUStructurePatterns.cpp:28-152, GPUNodePatterns.cpp:16-509).
 #pragma once
 #include <string>
+#include <vector>
 
 #include "plan.h"
 
@@ -37,6 +38,14 @@ struct EmitOptions {
   // second half where the fewest values are alive (fewer values through scratch, but a third more chunks and
   // with them more re-staged features: measured 89-92 ms against 86.8 ms on the 53 k-node model, so 0 is the default).
   int scopeCut = 0;
+  int stageUnroll = 12;             // scope-local staging: global loads a thread keeps in flight
+  int loadMode = 0;                // how the early request is made: 0 load, 1 L1 prefetch + load at the use, 2 volatile load
+  int prefetchSlots = 0;           // scope-local staging: operands of earlier chunks copied ahead into a shared-memory ring of this many slots (0: loaded at the use)
+  int rowStageUnroll = 8;          // row-major staging: global loads a thread keeps in flight
+  int chunkBarrier = 0;            // scope-local staging: 1 = CTA-wide barriers around every chunk's staging (all warps in lock step)
+  int fuseLeaves = 1;              // discrete leaf children of one product share a table over their combined code (see emit.cc)
+  int fuseEntries = 32;            // largest fused table, in entries
+  int loadAhead = 0;               // chunked kernels request an operand of an earlier chunk this many nodes before its first use
   int hoistLoads = 0;              // scope-local chunks request up to this many operands of earlier chunks at their top
   // Asynchronous double-buffered staging (float32 inputs that are all read as values, log space): tile t + 1 is
   // copied global -> shared with cp.async while tile t is evaluated.  Rows keep their order with an odd stride,
@@ -55,6 +64,8 @@ struct EmitInfo {
   int scratchSlots = 0;     // scratch values per CTA thread: cross-chunk values x tiles per group
   bool scoped = false;      // kernel reads a feature-major float copy:  (xt, out, n, tab, lut, scratch, ld)
   int numChunks = 1;
+  std::vector<double> fusedTable;   // entries that follow the plan's leaf tables in the kernel's table image
+  int fusedGroups = 0;
 };
 
 std::string emitCuda(const Plan& plan, const EmitOptions& opt, EmitInfo* info);

@@ -123,7 +123,7 @@ int dtypeCode(const FeatureType& t) {
 }
 
 // ---- plan file -----------------------------------------------------------------------------------
-const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '4'};
+const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '5'};
 
 struct Writer {
   std::vector<uint8_t> b;
@@ -153,13 +153,16 @@ std::string makeStatsJson(const Plan& p, Strategy s, const EmitInfo& ei, int reg
   o << base << ",\"log_space\":" << (p.logSpace ? "true" : "false") << ",\"strategy\":\""
     << (s == kUnrolled ? "unrolled" : (s == kInterpreter ? "interpreter" : "layered")) << "\",\"tile\":" << ei.tile << ",\"registers\":" << regs
     << ",\"spill_bytes\":" << spill << ",\"smem_bytes\":" << ei.dynamicSmemBytes << ",\"interp_slots\":" << interpSlots
-    << ",\"scratch_slots\":" << ei.scratchSlots << ",\"chunks\":" << ei.numChunks << ",\"scoped_staging\":" << (ei.scoped ? "true" : "false") << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"lut_bytes\":" << p.lut.size() << "}";
+    << ",\"scratch_slots\":" << ei.scratchSlots << ",\"chunks\":" << ei.numChunks << ",\"scoped_staging\":" << (ei.scoped ? "true" : "false") << ",\"table_entries\":" << (p.tabF32.size() + p.tabF64.size()) << ",\"fused_table_entries\":" << ei.fusedTable.size() << ",\"lut_bytes\":" << p.lut.size() << "}";
   return o.str();
 }
 
 void parallelCopy(void* dst, const void* src, size_t bytes) {
+  // up to half of the host's hardware threads (at most 12), 4 MB or more each: one thread moves about 5 GB/s,
+  // the copy engine behind it takes more than 50
   const size_t kMin = 4u << 20;
-  unsigned nt = (unsigned)std::min<size_t>(4, bytes / kMin);
+  const unsigned hw = std::max(8u, std::thread::hardware_concurrency());
+  unsigned nt = (unsigned)std::min<size_t>(std::min(12u, hw / 2), bytes / kMin);
   if (nt <= 1) {
     std::memcpy(dst, src, bytes);
     return;
@@ -228,13 +231,27 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-scope-bytes") o.scopeBytes = std::atoi(v.c_str());
     else if (k == "spnb-scope-cut") o.scopeCut = std::atoi(v.c_str());
     else if (k == "spnb-hoist-loads") o.hoistLoads = std::atoi(v.c_str());
+    else if (k == "spnb-load-ahead") o.loadAhead = std::atoi(v.c_str());
+    else if (k == "spnb-prefetch-slots") {
+      o.prefetchSlots = std::atoi(v.c_str());
+      if (o.prefetchSlots < 0 || o.prefetchSlots > 32) fail("spnb-prefetch-slots must be between 0 and 32");
+    }
+    else if (k == "spnb-row-stage-unroll") o.rowStageUnroll = std::atoi(v.c_str());
+    else if (k == "spnb-chunk-barrier") o.chunkBarrier = std::atoi(v.c_str());
+    else if (k == "spnb-fuse-leaves") o.fuseLeaves = std::atoi(v.c_str());
+    else if (k == "spnb-fuse-entries") o.fuseEntries = std::atoi(v.c_str());
+    else if (k == "spnb-load-mode") o.loadMode = std::atoi(v.c_str());
+    else if (k == "spnb-stage-unroll") o.stageUnroll = std::atoi(v.c_str());
     else if (k == "spnb-tc-tiles") {
       o.tcTiles = std::atoi(v.c_str());
       if (o.tcTiles != 1 && o.tcTiles != 2) fail("spnb-tc-tiles must be 1 or 2");
     } else if (k == "spnb-tc-rings") {
       o.tcRings = std::atoi(v.c_str());
-      if (o.tcRings != 0 && o.tcRings != 44 && o.tcRings != 43 && o.tcRings != 42 && o.tcRings != 33 && o.tcRings != 32)
-        fail("spnb-tc-rings must be 0 (automatic), 44, 43, 42, 33 or 32 (weight blocks and leaf stages in flight)");
+      if (o.tcRings != 0 && (o.tcRings / 10 < 2 || o.tcRings / 10 > 6 || o.tcRings % 10 < 2 || o.tcRings % 10 > 7))
+        fail("spnb-tc-rings must be 0 (automatic) or two digits: weight blocks (2-6) and leaf stages (2-7) in flight");
+    } else if (k == "spnb-tc-global-slots") {
+      o.tcGlobalSlots = std::atoi(v.c_str());
+      if (o.tcGlobalSlots < -1 || o.tcGlobalSlots > 8) fail("spnb-tc-global-slots must be -1 (automatic) or 0-8");
     } else if (k == "spnb-tc-fold") {
       if (v != "packed" && v != "scalar") fail("spnb-tc-fold must be packed or scalar");
       o.tcFoldScalar = v == "scalar" ? 1 : 0;
@@ -303,6 +320,14 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     eo.scopeBytes = opt.scopeBytes;
     eo.scopeCut = opt.scopeCut;
     eo.hoistLoads = opt.hoistLoads;
+    eo.loadAhead = opt.loadAhead;
+    eo.fuseLeaves = opt.fuseLeaves;
+    eo.fuseEntries = opt.fuseEntries;
+    eo.chunkBarrier = opt.chunkBarrier;
+    eo.rowStageUnroll = opt.rowStageUnroll;
+    eo.prefetchSlots = opt.prefetchSlots;
+    eo.loadMode = opt.loadMode;
+    eo.stageUnroll = opt.stageUnroll;
     source = emitCuda(plan, eo, &ei);
     if (ei.dynamicSmemBytes > 227 * 1024) fail("Generated kernel needs more shared memory than one SM has; use spnb-kernel=interp or a smaller spnb-tile");
     jr = jitCompile(source, m.name, opt.optLevel, opt.maxRegisters);
@@ -349,6 +374,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   w.blob(xspn.data(), xspn.size());
   w.str(source);
   w.blob(jr.cubin.data(), jr.cubin.size());
+  w.blob(reinterpret_cast<const uint8_t*>(ei.fusedTable.data()), ei.fusedTable.size() * sizeof(double));
   {
     std::ofstream f(planPath, std::ios::binary | std::ios::trunc);
     if (!f) fail("Could not write plan file " + planPath);
@@ -480,6 +506,11 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->source_ = r.str();
   std::vector<uint8_t> cubin = r.blob();
   e->cubin_.assign(cubin.begin(), cubin.end());
+  {
+    std::vector<uint8_t> ft = r.blob();
+    e->emitInfo_.fusedTable.resize(ft.size() / sizeof(double));
+    if (!ft.empty()) std::memcpy(e->emitInfo_.fusedTable.data(), ft.data(), e->emitInfo_.fusedTable.size() * sizeof(double));
+  }
   e->model_ = readXspnBytes(xspn.data(), xspn.size());
   e->plan_ = buildPlan(e->model_, opt.logSpace);
   e->emitInfo_.kernelName = "spnb_kernel";
@@ -493,6 +524,7 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->selftestWithhold_ = opt.selftestWithhold;
   e->tcFoldScalar_ = opt.tcFoldScalar;
   e->tcRings_ = opt.tcRings;
+  e->tcGlobalSlots_ = opt.tcGlobalSlots;
   // layered models run on the tensor-memory kernel unless another layered kernel is asked for by name
   e->layeredTcf_ = opt.kernelMode != "layered-scalar" && opt.kernelMode != "layered-mma";
   e->meta_.kernelName = e->model_.name;
@@ -554,7 +586,19 @@ Engine::DeviceState& Engine::state(int device) {
     if (bytes) CUDA_OK(cudaMemcpy(d, src, bytes, cudaMemcpyHostToDevice));
     return d;
   };
-  if (p.logSpace) st->dTab = upload(p.tabF32.data(), p.tabF32.size() * 4);
+  // the generated kernel's table image: the plan's leaf tables, then the fused tables the emitter added
+  const std::vector<double>& fusedTab = emitInfo_.fusedTable;
+  if (strategy_ == kUnrolled && !fusedTab.empty()) {
+    if (p.logSpace) {
+      std::vector<float> img(p.tabF32);
+      for (double v : fusedTab) img.push_back((float)v);
+      st->dTab = upload(img.data(), img.size() * 4);
+    } else {
+      std::vector<double> img(p.tabF64);
+      img.insert(img.end(), fusedTab.begin(), fusedTab.end());
+      st->dTab = upload(img.data(), img.size() * 8);
+    }
+  } else if (p.logSpace) st->dTab = upload(p.tabF32.data(), p.tabF32.size() * 4);
   else st->dTab = upload(p.tabF64.data(), p.tabF64.size() * 8);
   st->dLut = upload(p.lut.data(), p.lut.size());
   if (strategy_ == kUnrolled) {
@@ -792,21 +836,35 @@ Engine::DeviceState& Engine::state(int device) {
             std::vector<float>& centres4 = prog.centres4;
             const size_t ns = ds.size();
             const int maxDepth = prog.aSlots, depth = 0;
-            // Ring depths (weight blocks, leaf stages in flight): the deepest pair that fits, or the one asked for.
-            // With three or more pending left operands the outermost one (written and read once per repetition)
-            // is kept in global memory, which buys the rings 33 KB of shared memory.
-            int ring = 0, leafRing = 0;
-            const int globalSlots = maxDepth >= 3 ? 1 : 0;
-            const int smemSlots = std::max(maxDepth - globalSlots, 1);
-            static const int kRings[][2] = {{4, 4}, {4, 3}, {4, 2}, {3, 3}, {3, 2}};
-            for (auto& cand : kRings) {
-              if (ring) break;
-              if (tcRings_ > 0 && (cand[0] != tcRings_ / 10 || cand[1] != tcRings_ % 10)) continue;
-              if (layeredDualSmemBytes(smemSlots, cand[0], cand[1]) <= (size_t)prop.sharedMemPerBlockOptin) {
-                ring = cand[0];
-                leafRing = cand[1];
+            // Ring depths (weight blocks, leaf stages in flight) and where the pending left operands wait.  Measured
+            // on the 784-feature model (ms per 2 M samples): 4 + 4 with one pending operand in global memory 201.4,
+            // 5 + 4 201.3, 4 + 5 197.0; with all but the innermost pending operand in global memory (33 KB more
+            // shared memory for the rings) 4 + 7 187.2, 5 + 6 193.0, 6 + 5 198.0: leaf stages in flight are what pays.
+            int ring = 0, leafRing = 0, globalSlots = 0;
+            struct Cand { int ring, leafRing, globalSlots; };
+            std::vector<Cand> cands;
+            if (tcRings_ > 0) {
+              const int g = tcGlobalSlots_ >= 0 ? tcGlobalSlots_ : (maxDepth >= 3 ? 1 : 0);
+              cands.push_back({tcRings_ / 10, tcRings_ % 10, g});
+            } else {
+              const int gDeep = std::max(maxDepth - 1, 0), gOne = maxDepth >= 3 ? 1 : 0;
+              for (int g : {gDeep, gOne}) {
+                if (tcGlobalSlots_ >= 0 && g != gDeep) continue;
+                const int gg = tcGlobalSlots_ >= 0 ? tcGlobalSlots_ : g;
+                for (int lr : {7, 6, 5, 4, 3, 2}) cands.push_back({4, lr, gg});
+                for (int lr : {3, 2}) cands.push_back({3, lr, gg});
               }
             }
+            for (const Cand& c : cands) {
+              const int g = std::min(c.globalSlots, std::max(maxDepth - 1, 0));
+              if (layeredDualSmemBytes(std::max(maxDepth - g, 1), c.ring, c.leafRing) <= (size_t)prop.sharedMemPerBlockOptin) {
+                ring = c.ring;
+                leafRing = c.leafRing;
+                globalSlots = g;
+                break;
+              }
+            }
+            const int smemSlots = std::max(maxDepth - globalSlots, 1);
             if (ring && depth == 0) {
               if (cols4.empty()) { cols4.assign(8, 0); centres4.assign(8, 0.f); }
               // per sum the largest weight of its row, the multiplier form of the log2 scales

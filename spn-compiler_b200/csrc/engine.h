@@ -44,10 +44,19 @@ struct Options {
   int scoped = -1;             // "spnb-scoped": scope-local staging of a chunked generated kernel (-1 automatic, 0 off, 1 on)
   int asyncStage = 1;          // "spnb-async-stage": 0 = never stage the next tile with cp.async while one is evaluated
   int scopeCut = 0;            // "spnb-scope-cut": 1 = end scope-local chunks where the fewest values are alive
+  int stageUnroll = 12;         // "spnb-stage-unroll": unroll factor of the scope-local staging loops
+  int loadMode = 0;            // "spnb-load-mode": 0 early load, 1 L1 prefetch and load at the first use, 2 early volatile load
+  int prefetchSlots = 0;       // "spnb-prefetch-slots": depth of the shared-memory ring operands of earlier chunks are copied into ahead of their use
+  int rowStageUnroll = 8;      // "spnb-row-stage-unroll": unroll factor of the row-major staging loop
+  int chunkBarrier = 0;        // "spnb-chunk-barrier": 1 = CTA-wide barriers around every chunk's staging with scope-local staging
+  int fuseLeaves = 1;          // "spnb-fuse-leaves": fused tables for the discrete leaf children of a product
+  int fuseEntries = 32;        // "spnb-fuse-entries": largest fused table, in entries
+  int loadAhead = 0;           // "spnb-load-ahead": nodes between the request of an earlier chunk's value and its first use
   int hoistLoads = 0;          // "spnb-hoist-loads": operands of earlier chunks a scope-local chunk requests at its top
   int scopeBytes = 0;          // "spnb-scope-bytes": staged bytes per sample and chunk (0 = what fits)
   int tcTiles = 2;             // "spnb-tc-tiles": 2 = two sample tiles per CTA where the model allows it, 1 = one tile
-  int tcRings = 0;             // "spnb-tc-rings": weight blocks and leaf stages in flight in the two-tile kernel (43, 42, 33, 32; 0 = deepest that fits)
+  int tcRings = 0;             // "spnb-tc-rings": two digits, weight blocks (2-6) and leaf stages (2-7) in flight in the two-tile kernel; 0 = automatic
+  int tcGlobalSlots = -1;      // "spnb-tc-global-slots": pending left operands per tile kept in global instead of shared memory; -1 = automatic
   int tcFoldScalar = 0;        // "spnb-tc-fold": packed (fma.rn.f32x2, default) or scalar FMAs in the two-tile kernel's fold
   long long spinLimit = 0;     // "spnb-spin-limit": polls after which a tensor-core barrier wait gives up (0 = 2^17, about a second)
   int selftestWithhold = 0;    // "spnb-selftest-withhold-commit": 1 = the two-tile kernel leaves out one commit (tests
@@ -109,6 +118,7 @@ class Engine {
   int selftestWithhold_ = 0;
   int tcFoldScalar_ = 0;
   int tcRings_ = 0;
+  int tcGlobalSlots_ = -1;
   bool layeredTcf_ = false;
   std::string source_;
   std::vector<char> cubin_;

@@ -60,24 +60,31 @@ constexpr int KSTEP_B = NBLK * 16 * 2;  // 4096 B
 constexpr int B_BLOCK = 4 * KSTEP_B;    // 16 KB: value j 0..15, value j 16..31, residue j 0..15, residue j 16..31
 constexpr int KSTEP_BL = KMAX * 16 * 2; // 1024 B: leaf weights of one k-step (two features)
 constexpr int LW_STAGE = 4 * KSTEP_BL;  // 4 KB: eight features
-constexpr int LW_RING_MAX = 4;
+constexpr int W_RING_MAX = 6;            // weight blocks in flight, at most
+constexpr int LW_RING_MAX = 7;           // leaf stages in flight, at most (tensor-memory columns for their operand rows)
 // one leaf ring slot: the stage's weights, its eight features' inputs for the 256 samples of the tile pair,
 // its eight centres (padded to 128 bytes)
 constexpr int LEAF_X = STAGE_FEATS * NTILE * TS * 4;
 constexpr int LEAF_SLOT_TX = LW_STAGE + LEAF_X + STAGE_FEATS * 4;
 constexpr int LEAF_SLOT = LW_STAGE + LEAF_X + 128;
 constexpr int SLOT_FLOATS = (KMAX + 1) * TS;  // one a-stack slot: [32][128] normalised values, then [128] log2 scales
+// Tensor-memory columns (relative to the tile's first accumulator) of the operand rows of the leaf stage in ring
+// slot `slot`: slots 0-3 fill the second accumulator, slots 4-6 the columns of the first accumulator behind the
+// 32 a leaf region accumulates into.  No inner region is in flight on the tile while a leaf region runs.
+__device__ __forceinline__ unsigned leafOperandCol(unsigned slot) {
+  return slot < 4u ? (unsigned)NBLK + slot * STAGE_COLS : (slot - 3u) * STAGE_COLS;
+}
 constexpr float kHalfRange = 240.f;     // |x'| below this: x'^2 < 65504
 constexpr int TMEM_COLS = 512;
 
 // barrier indices
-constexpr int BAR_TILE = 9;             // per tile: opReady, accFull[2], accFree[2], leafFull[4]
+constexpr int BAR_TILE = 5 + LW_RING_MAX; // per tile: opReady, accFull[2], accFree[2], leafFull[LW_RING_MAX]
 constexpr int BAR_OPREADY = 0, BAR_ACCFULL = 1, BAR_ACCFREE = 3, BAR_LEAFFULL = 5;
 constexpr int BAR_LEAFDONE = NTILE * BAR_TILE;         // [2]
-constexpr int BAR_WFULL = BAR_LEAFDONE + NTILE;        // [4] weight block landed
-constexpr int BAR_WEMPTY = BAR_WFULL + 4;              // [4] both tiles' MMAs on the block done (two commits)
-constexpr int BAR_LWFULL = BAR_WEMPTY + 4;             // [4] leaf stage (weights, inputs, centres) landed
-constexpr int BAR_LWEMPTY = BAR_LWFULL + LW_RING_MAX;  // [4] both tiles' MMAs on the stage done (two commits)
+constexpr int BAR_WFULL = BAR_LEAFDONE + NTILE;        // [W_RING_MAX] weight block landed
+constexpr int BAR_WEMPTY = BAR_WFULL + W_RING_MAX;     // [W_RING_MAX] both tiles' MMAs on the block done (two commits)
+constexpr int BAR_LWFULL = BAR_WEMPTY + W_RING_MAX;    // [LW_RING_MAX] leaf stage (weights, inputs, centres) landed
+constexpr int BAR_LWEMPTY = BAR_LWFULL + LW_RING_MAX;  // [LW_RING_MAX] both tiles' MMAs on the stage done (two commits)
 constexpr int BAR_DRAIN = BAR_LWEMPTY + LW_RING_MAX;   // [2] per issuer
 constexpr int NBARS = BAR_DRAIN + NTILE;
 
@@ -298,9 +305,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
       mbarInit(bar(BAR_LEAFDONE + t), 1);
       mbarInit(bar(BAR_DRAIN + t), 1);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < W_RING_MAX; ++i) {
       mbarInit(bar(BAR_WFULL + i), 1);
       mbarInit(bar(BAR_WEMPTY + i), NTILE);
+    }
+    for (int i = 0; i < LW_RING_MAX; ++i) {
       mbarInit(bar(BAR_LWFULL + i), 1);
       mbarInit(bar(BAR_LWEMPTY + i), NTILE);
     }
@@ -434,7 +443,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
               }
               // operand rows of this stage: tensor-memory columns of the tile's second accumulator, which no
               // inner region uses while a leaf region runs (feature 2 j, 2 j + 1 = the 16 K entries of MMA j)
-              tmemStore32(tmemAcc + NBLK + leafRing * STAGE_COLS, rowsA);
+              tmemStore32(tmemAcc + leafOperandCol(leafRing), rowsA);
               PROF_ADD(P_W_LEAF_BUILD, tb);
               fenceBefore();
               __syncwarp();
@@ -651,7 +660,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) layeredDualKernel(DualArgs a, con
             PROF_ADD(P_I_WAIT_LEAFFULL, tq3);
             if (lane == 0) {
               fenceAfter();
-              const unsigned arows = acc + NBLK + leafRing * STAGE_COLS;   // operand rows written by the workers
+              const unsigned arows = acc + leafOperandCol(leafRing);   // operand rows written by the workers
               const unsigned long long lwd = lwDesc0 + (unsigned)((leafRing * LEAF_SLOT) >> 4);
 #pragma unroll
               for (int ks = 0; ks < STAGE_FEATS / 2; ++ks)

@@ -187,6 +187,41 @@ def test_histogram_buckets_can_be_computed_where_that_is_exact(tmp_path):
     assert src2.count(") >> 16;") == 1 and "lut_s" in src2
 
 
+def test_discrete_leaves_of_a_product_share_a_fused_table(tmp_path):
+    """Categorical leaf children of one product are looked up through one table over their combined code
+    (fewer shared-memory reads); a leaf with a second consumer, a Gaussian sibling and a chunked kernel keep
+    the plain reads.  (Compilation needs no GPU.)"""
+    from spnb import capi, synth
+    b = synth.FlatSPN(4, "int32", "fusable")
+    c0 = b.categorical(0, [0.2, 0.8])
+    c1 = b.categorical(1, [0.5, 0.25, 0.25])
+    c2 = b.categorical(2, [0.1, 0.9])
+    c3 = b.categorical(3, [0.3, 0.7])
+    d3 = b.categorical(3, [0.6, 0.4])
+    shared = b.categorical(2, [0.4, 0.6])
+    p1 = b.product([c0, c1, c2, c3])
+    p2 = b.product([b.categorical(0, [0.5, 0.5]), b.categorical(1, [0.1, 0.1, 0.8]), shared, d3])
+    p3 = b.product([b.categorical(0, [0.3, 0.7]), b.categorical(1, [0.2, 0.2, 0.6]), shared, b.categorical(3, [0.9, 0.1])])
+    b.root = b.sum([p1, p2, p3], [0.5, 0.25, 0.25])
+    q = write_query(b, False, directory=str(tmp_path))
+    for log_space in ("true", "false"):
+        on, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": log_space, "spnb-kernel": "unrolled",
+                                       "spnb-fuse-entries": "128"})
+        off, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": log_space, "spnb-kernel": "unrolled",
+                                        "spnb-fuse-leaves": "0"})
+        pon, poff = capi.Plan(on), capi.Plan(off)
+        ld = "ld.shared.f32" if log_space == "true" else "ld.shared.f64"
+        # 11 leaves read one by one; fused: one group of three per product (4 * 5 * 4 = 80 combined codes each; a
+        # fourth leaf would exceed the 128-entry limit), the first product's last leaf and the shared leaf on their own
+        assert poff.source.count(ld) == 11 and poff.stats["fused_table_entries"] == 0
+        assert pon.source.count(ld) == 3 + 2
+        assert pon.stats["fused_table_entries"] == 3 * 80
+    small, _ = capi.compile_query(q, {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "unrolled",
+                                      "spnb-fuse-entries": "20"})
+    # pairs only: (4 * 5) + (4 * 4) in the first product, (4 * 5) in the other two
+    assert capi.Plan(small).stats["fused_table_entries"] == 36 + 20 + 20
+
+
 def test_two_tile_tensor_core_program(tmp_path):
     """The plan of a full-width layered model is annotated for the two-tile tensor-core kernel: right operands
     go straight to the operand buffer, left operands wait in registers (sibling = one leaf region) or in an

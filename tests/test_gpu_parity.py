@@ -110,17 +110,19 @@ def test_scope_local_staging(capi, tmp_path):
     pieces the feature-major copy is made in."""
     name, spn, inputs, log_space, marginal = small_configs()[4]
     q = write_query(spn, marginal, directory=str(tmp_path))
-    for budget, chunk in ((0, 2000), (64, 300), (16, 97)):
-        # the middle variant also ends its chunks where the fewest values are alive and requests the operands
-        # of earlier chunks at the top of each function
+    for budget, chunk, ring in ((0, 2000, 0), (64, 300, 0), (16, 97, 0), (40, 300, 4), (0, 2000, 12)):
+        # the second variant also ends its chunks where the fewest values are alive and requests the operands
+        # of earlier chunks at the top of each function; the last two copy the operands of earlier chunks into a
+        # shared-memory ring ahead of their use
         plan_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="unrolled", spnb_scoped=1, spnb_scope_bytes=budget,
                                                    spnb_chunk_nodes=chunk, spnb_table_window=4096,
                                                    spnb_scope_cut=1 if budget == 64 else 0,
-                                                   spnb_hoist_loads=24 if budget == 64 else 0))
+                                                   spnb_hoist_loads=24 if budget == 64 else 0,
+                                                   spnb_prefetch_slots=ring))
         plan = capi.Plan(plan_path)
         st = plan.stats
         assert st["scoped_staging"] and st["tile"] == 1024 and st["chunks"] > 1
-        for n in (1, 1025, 70001) + ((2 * 524288 + 777,) if budget == 64 else ()):
+        for n in (1, 1025, 70001) + ((2 * 524288 + 777,) if budget in (64, 40) else ()):
             x = inputs(n)
             x[::5, 3] = np.nan        # Gaussian column
             x[::7, 200] = np.nan      # categorical column
@@ -299,6 +301,35 @@ def test_histogram_buckets_by_arithmetic(capi, tmp_path):
         assert err <= REL_TOL_F32, (extra, err)
         plan.close()
         os.remove(plan_path)
+
+
+def test_fused_leaf_tables(capi, tmp_path):
+    """Discrete leaf children of a product read through one table over their combined code must give what the
+    one-read-per-leaf kernel gives (to rounding) and what the oracle gives, in both spaces, with codes outside the
+    tables and, for floating inputs with marginal support, missing values."""
+    name, spn, inputs, _, _ = small_configs()[0]
+    for log_space, marginal, ftype in ((False, False, "int32"), (True, False, "int32"), (True, True, "float32"), (False, True, "float64")):
+        spn.feature_type = ftype
+        q = write_query(spn, marginal, directory=str(tmp_path))
+        x = inputs(20011).astype(ftype)
+        x[::7, 3] = 7            # a category no table has: impossible evidence
+        x[::11, 5] = -1
+        if marginal:
+            x[::5, 2] = np.nan
+            x[::13, :] = np.nan
+        want = oracle_eval(q, x, log_space)
+        got = {}
+        for fuse, entries in ((1, 128), (1, 16), (0, 128)):
+            plan_path, _ = capi.compile_query(q, _opts(log_space, spnb_kernel="unrolled", spnb_fuse_leaves=fuse, spnb_fuse_entries=entries))
+            plan = capi.Plan(plan_path)
+            assert (plan.stats["fused_table_entries"] > 0) == bool(fuse)
+            got[(fuse, entries)] = plan.execute_host(x)
+            err = max_rel_err(got[(fuse, entries)], want)
+            assert err <= (REL_TOL_F32 if log_space else REL_TOL_F64), (log_space, marginal, fuse, entries, err)
+            plan.close()
+            os.remove(plan_path)
+        assert max_rel_err(got[(1, 128)], got[(0, 128)]) <= (2e-6 if log_space else 1e-14)
+    spn.feature_type = "int32"
 
 
 def test_streamed_table_window(capi, tmp_path):
