@@ -112,13 +112,15 @@ def test_scope_local_staging(capi, tmp_path):
     q = write_query(spn, marginal, directory=str(tmp_path))
     for budget, chunk, ring in ((0, 2000, 0), (64, 300, 0), (16, 97, 0), (40, 300, 4), (0, 2000, 12)):
         # the second variant also ends its chunks where the fewest values are alive and requests the operands
-        # of earlier chunks at the top of each function; the last two copy the operands of earlier chunks into a
-        # shared-memory ring ahead of their use
+        # of earlier chunks at the top of each function; the third keeps CTA-wide barriers between its chunks (the
+        # others let the warps drift apart); the last two copy the operands of earlier chunks into a shared-memory
+        # ring ahead of their use
         plan_path, _ = capi.compile_query(q, _opts(True, spnb_kernel="unrolled", spnb_scoped=1, spnb_scope_bytes=budget,
                                                    spnb_chunk_nodes=chunk, spnb_table_window=4096,
                                                    spnb_scope_cut=1 if budget == 64 else 0,
                                                    spnb_hoist_loads=24 if budget == 64 else 0,
-                                                   spnb_prefetch_slots=ring))
+                                                   spnb_prefetch_slots=ring,
+                                                   spnb_chunk_barrier=1 if budget == 16 else 0))
         plan = capi.Plan(plan_path)
         st = plan.stats
         assert st["scoped_staging"] and st["tile"] == 1024 and st["chunks"] > 1
