@@ -197,6 +197,8 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     tableLimit = std::min<size_t>((size_t)opt.smemTableLimit, 32 * 1024);
   }
   const int SX = scoped ? TILE : TILE + 1;   // the transposing store of the row-major path needs the padding
+  // scope-local staging: the discrete features' codes come ready-made from a plane behind the feature-major copy
+  const bool codePlane = scoped && opt.codePlane != 0 && p.numCodeSlots > 0;
   // Leaf tables are always read from shared memory.  Tables larger than the window are streamed
   // through it: leaves appear in the body in table order, so at the points where the next leaf's
   // table lies beyond the window the CTA reloads the window from global memory between two barriers.
@@ -221,8 +223,15 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   const size_t asyncBuf = ((size_t)TILE * RS * 4 + 15) & ~size_t(15);
   // every input is read as a value by Gaussian leaves (no staged codes, no leaf tables): the body indexes a
   // staged row by the feature itself
-  const bool asyncStage = opt.asyncStage != 0 && !scoped && NC == 0 && NV > 0 && tabEntries == 0 && lg && floatIn &&
-                          p.ftype.bits == 32 && opt.groupTiles <= 1 && 2 * asyncBuf + 64 <= 226 * 1024;
+  // ... or the model has discrete leaves whose tables stay resident in shared memory: the rows are staged raw
+  // (32-bit inputs), every body function digests the discrete features it reads into codes once, in registers
+  // (at most 27 features fit two buffers of 1024 rows), and the tables sit behind the two buffers
+  bool asyncDiscrete = NC > 0 && !anyClamp && !streamed && (lutBytes == 0 || lutSmem) && (lg ? floatIn || NV == 0 : NV == 0);
+  for (const IndexGroup& g : p.groups) asyncDiscrete = asyncDiscrete && g.mode != kGeneric;
+  const size_t asyncTables = (tabSmem ? winBytes : 0) + (lutSmem ? p.lut.size() + 4 : 0) + 32;
+  const bool asyncStage = opt.asyncStage != 0 && !scoped && p.ftype.bits == 32 && opt.groupTiles <= 1 &&
+                          ((NC == 0 && NV > 0 && tabEntries == 0 && lg && floatIn) || asyncDiscrete) &&
+                          2 * asyncBuf + 64 + asyncTables <= 226 * 1024;
   const bool nanFlagsWanted = p.marginal && floatIn && NV > 0 && p.stats.gauss > 0;
 
   // ---- chunks: consecutive stretches of the evaluation order, one generated function each -----------------
@@ -416,7 +425,12 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   auto readX = [&](const std::string& dst, int slot, long long node) {
     return ldsStmt("real_t", ldReal, cReal, dst, "xs_t", asyncStage ? (long long)rb * slot : (long long)rb * slot * SX, mergeX ? -1 : node);
   };
+  std::vector<int> featureOfCodeSlot(NC > 0 ? NC : 0, -1);
+  for (int f = 0; f < F; ++f)
+    if (p.features[f].codeSlot >= 0 && p.features[f].codeSlot < NC) featureOfCodeSlot[p.features[f].codeSlot] = f;
   auto readCode = [&](const std::string& dst, int slot, long long node) {
+    // asynchronous staging: the code was digested from the raw row at the top of the function
+    if (asyncStage) return "  const int " + dst + " = cf" + std::to_string(featureOfCodeSlot[slot]) + ";\n";
     return ldsStmt("int", cb == 1 ? "ld.shared.u8" : "ld.shared.u16", "r", dst, "cs_t", (long long)cb * slot * SX, node);
   };
   long long winBase = 0;  // first table entry held by the window at the current point of the body
@@ -567,7 +581,21 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   o << "static __device__ __noinline__ out_t " << fname << "(const unsigned xs_s, const unsigned cs_s, const unsigned tab_s, "
        "const unsigned lut_s, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, uint4* __restrict__ win, "
        "real_t* __restrict__ sc, const unsigned tid)\n{\n";
-  o << "  const unsigned xs_t = xs_s + " << (asyncStage ? rb * RS : rb) << "u * tid;\n  const unsigned cs_t = cs_s + " << cb << "u * tid;\n";
+  o << "  const unsigned xs_t = xs_s + " << (asyncStage ? 4 * RS : rb) << "u * tid;\n  const unsigned cs_t = cs_s + " << cb << "u * tid;\n";
+  if (asyncStage && NC > 0) {
+    // codes of the discrete features, from this thread's raw row (unused ones are dropped by the compiler)
+    for (int f = 0; f < F; ++f) {
+      const FeatureMeta& fm = p.features[f];
+      if (fm.codeSlot < 0) continue;
+      o << "  int cf" << f << "; { unsigned raw; asm(\"ld.shared.b32 %0, [%1+" << 4 * f << "];\" : \"=r\"(raw) : \"r\"(xs_t));\n";
+      if (floatIn) o << "    const float rf = __uint_as_float(raw); const unsigned rr = (unsigned)__float2int_rz(rf) - " << (unsigned)fm.lo << "u;\n";
+      else if (p.ftype.kind == InKind::UInt) o << "    const unsigned rr = (raw > 2147483647u ? 2147483647u : raw) - " << (unsigned)fm.lo << "u;\n";
+      else o << "    const unsigned rr = raw - " << (unsigned)fm.lo << "u;\n";
+      o << "    cf" << f << " = rr < " << (unsigned)fm.domain << "u ? (int)rr + 2 : 1;";
+      if (floatIn) o << " if (rf != rf) cf" << f << " = 0;";
+      o << " }\n";
+    }
+  }
   // both variants of a chunk leave the same table window behind; a variant that skips a chunk (no staged
   // values: nothing NaN-sensitive in it) continues from what the plain body of that chunk leaves
   winBase = chunk == 0 ? 0 : winEnd[chunk - 1];
@@ -784,6 +812,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       // (domain stored as -domain - 1: the feature's special codes are the clamped ones)
       for (int32_t f : chunkCodeFeat[c]) {
         const FeatureMeta& fm = p.features[f];
+        if (codePlane) { o << (cfN ? "," : "") << fm.codeSlot; ++cfN; continue; }   // its row of the code plane
         o << (cfN ? "," : "") << f << "," << fm.lo << "," << (clampAllowed && fm.clampCodes ? -fm.domain - 1 : fm.domain);
         cfN += 3;
       }
@@ -793,13 +822,18 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     // One staging routine for all chunks, out of line: the kernel below stays a short list of calls (the
     // JIT's time grows quadratically with the memory operations it sees in one function).
     o << "typedef " << (cb == 1 ? "unsigned char" : "unsigned short") << " code_t;\n";
-    o << "static __device__ __noinline__ int spnb_stage(unsigned char* __restrict__ smem, const float* __restrict__ src, const unsigned long long ld,\n"
+    o << "static __device__ __noinline__ int spnb_stage(unsigned char* __restrict__ smem, const float* __restrict__ src, const code_t* __restrict__ srcc, const unsigned long long ld,\n"
          "                                              const int* __restrict__ cf, const int nv, const int nc, const unsigned codeBase, const unsigned tid)\n{\n";
     o << "  float* xs = reinterpret_cast<float*>(smem);\n  code_t* cs = reinterpret_cast<code_t*>(smem + codeBase);\n  int nan = 0;\n";
     o << "#pragma unroll " << std::max(opt.stageUnroll, 1) << "\n";
     o << "  for (int j = 0; j < nv; ++j) { const float raw = src[(unsigned long long)__ldg(cf + j) * ld]; xs[j * SX + tid] = raw; nan |= (raw != raw); }\n";
     o << "  cf += nv;\n";
     o << "#pragma unroll " << std::max(opt.stageUnroll, 1) << "\n";
+    if (codePlane) {
+      // the codes were made with the feature-major copy: one byte (half-word) per sample and feature
+      o << "  for (int j = 0; j < nc; ++j) cs[j * SX + tid] = srcc[(unsigned long long)__ldg(cf + j) * ld];\n";
+      o << "  return nan;\n}\n";
+    } else {
     o << "  for (int j = 0; j < nc; ++j) {\n";
     o << "    const float raw = src[(unsigned long long)__ldg(cf + 3 * j) * ld];\n";
     o << "    const unsigned rr = (unsigned)TOINT(raw) - (unsigned)__ldg(cf + 3 * j + 1);\n";
@@ -810,6 +844,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "    if (raw != raw) code = cl ? 65535 : 0;\n";
     o << "    cs[j * SX + tid] = (code_t)code;\n";
     o << "  }\n  return nan;\n}\n";
+    }
     o << "extern \"C\" __global__ void __launch_bounds__(TILE, 1)\n";
     o << "spnb_kernel(const float* __restrict__ xt, out_t* __restrict__ out, unsigned long long n, const real_t* __restrict__ tab_g, const unsigned char* __restrict__ lut_g, real_t* __restrict__ scratch, unsigned long long ld)\n{\n";
     if (nCross > 0) o << "  real_t* sc = scratch + ((size_t)blockIdx.x * " << (size_t)nCross * (size_t)groupTiles << "u * TILE + threadIdx.x);\n";
@@ -848,6 +883,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       o << "      const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
       o << "      // threads past the end of the batch repeat its last sample; their result is not stored\n";
       o << "      const float* __restrict__ src = xt + base + (tid < rows ? tid : rows - 1);\n";
+      o << "      const code_t* __restrict__ srcc = reinterpret_cast<const code_t*>(xt + (unsigned long long)NF * ld) + base + (tid < rows ? tid : rows - 1);\n";
       o << "      real_t* sct = sc + (size_t)t * " << nCross << "u * TILE;\n";
       // Thread = sample on both sides of the staging area: a thread stages and reads its own column only, so
       // the chunks need no CTA-wide barrier between them.  Without one the warps drift apart and one warp's
@@ -858,7 +894,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       const std::string anyNan = barrier ? "__syncthreads_or(nan)" : "__any_sync(0xffffffffu, nan)";
       if (barrier) o << "      __syncthreads();\n";
       const bool choose = twoBodies && nv > 0;
-      o << "      " << (choose ? "const int nan = " : "") << "spnb_stage(smem_raw, src, ld, CF + " << cfOff[c] << ", " << nv << ", " << nc << ", "
+      o << "      " << (choose ? "const int nan = " : "") << "spnb_stage(smem_raw, src, srcc, ld, CF + " << cfOff[c] << ", " << nv << ", " << nc << ", "
         << codeBase(c) << "u, tid);\n";
       const std::string args = "(xs_s, xs_s + " + std::to_string(codeBase(c)) + "u, tab_s, lut_s, tab_g, lut_g, win, sct, tid);\n";
       const bool last = c + 1 == nChunks;
@@ -891,6 +927,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       info->dynamicSmemBytes = smemTotal;
       info->scratchSlots = nCross * groupTiles;
       info->scoped = true;
+      info->codePlaneBytes = codePlane ? cb : 0;
       info->numChunks = (int)nChunks;
     }
     return o.str();
@@ -908,6 +945,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "  const unsigned tid = threadIdx.x;\n";
     o << "  const unsigned buf_s = (unsigned)__cvta_generic_to_shared(smem_raw);\n";
     o << "  uint4* win = reinterpret_cast<uint4*>(smem_raw + " << offTab << ");\n";
+    o << "  unsigned tab_s = 0, lut_s = 0;\n";
     o << "  const unsigned long long ntiles = (n + TILE - 1) / TILE;\n";
     o << "  // copy of one tile: element e of the tile's row-major block goes to word (e / NF) * RS + e % NF\n";
     o << "  auto issue = [&](unsigned long long tile, unsigned buf) {\n";
@@ -924,6 +962,16 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "    asm volatile(\"cp.async.commit_group;\" ::: \"memory\");\n";
     o << "  };\n";
     o << "  if (blockIdx.x < ntiles) issue(blockIdx.x, 0u);\n";
+    // (the tables are fetched while the first tile's copies are in flight)
+    if (tabSmem) {
+      // resident leaf tables behind the two buffers; the first barrier of the tile loop orders them before any read
+      o << "  tab_s = (unsigned)__cvta_generic_to_shared(win);\n";
+      o << "  for (unsigned i = tid; i < NTAB; i += TILE) reinterpret_cast<real_t*>(win)[i] = tab_g[i];\n";
+    }
+    if (lutSmem) {
+      o << "  { unsigned char* lut = smem_raw + " << offLut << ";\n";
+      o << "    for (unsigned i = tid; i < NLUT; i += TILE) lut[i] = lut_g[i];\n    lut_s = (unsigned)__cvta_generic_to_shared(lut); }\n";
+    }
     o << "  unsigned cur = 0;\n";
     o << "#pragma unroll 1\n";
     o << "  for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
@@ -936,7 +984,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "    out_t res;\n";
     auto chainA = [&](const char* prefix, const std::string& in2) {
       for (size_t c = 0; c < nChunks; ++c)
-        o << in2 << (c + 1 == nChunks ? "res = " : "") << prefix << c << "(xs_s, 0u, 0u, 0u, tab_g, lut_g, win, sc, tid);\n";
+        o << in2 << (c + 1 == nChunks ? "res = " : "") << prefix << c << "(xs_s, 0u, tab_s, lut_s, tab_g, lut_g, win, sc, tid);\n";
     };
     if (twoBodies) {
       o << "    int nan = 0;\n";

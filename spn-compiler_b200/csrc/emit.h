@@ -45,6 +45,7 @@ struct EmitOptions {
   int chunkBarrier = 0;            // scope-local staging: 1 = CTA-wide barriers around every chunk's staging (all warps in lock step)
   int fuseLeaves = 1;              // discrete leaf children of one product share a table over their combined code (see emit.cc)
   int fuseEntries = 32;            // largest fused table, in entries
+  int codePlane = 1;               // scope-local staging: discrete features are staged from a plane of ready-made codes
   int loadAhead = 0;               // chunked kernels request an operand of an earlier chunk this many nodes before its first use
   int hoistLoads = 0;              // scope-local chunks request up to this many operands of earlier chunks at their top
   // Asynchronous double-buffered staging (float32 inputs that are all read as values, log space): tile t + 1 is
@@ -64,6 +65,7 @@ struct EmitInfo {
   int scratchSlots = 0;     // scratch values per CTA thread: cross-chunk values x tiles per group
   bool scoped = false;      // kernel reads a feature-major float copy:  (xt, out, n, tab, lut, scratch, ld)
   int numChunks = 1;
+  int codePlaneBytes = 0;   // > 0: the kernel reads staged codes of this width from a plane behind the feature-major copy
   std::vector<double> fusedTable;   // entries that follow the plan's leaf tables in the kernel's table image
   int fusedGroups = 0;
 };

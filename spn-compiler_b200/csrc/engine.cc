@@ -123,7 +123,7 @@ int dtypeCode(const FeatureType& t) {
 }
 
 // ---- plan file -----------------------------------------------------------------------------------
-const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '5'};
+const char kMagic[8] = {'S', 'P', 'N', 'B', 'P', 'L', 'N', '6'};
 
 struct Writer {
   std::vector<uint8_t> b;
@@ -240,6 +240,7 @@ Options parseOptions(const std::vector<std::pair<std::string, std::string>>& kv)
     else if (k == "spnb-chunk-barrier") o.chunkBarrier = std::atoi(v.c_str());
     else if (k == "spnb-fuse-leaves") o.fuseLeaves = std::atoi(v.c_str());
     else if (k == "spnb-fuse-entries") o.fuseEntries = std::atoi(v.c_str());
+    else if (k == "spnb-code-plane") o.codePlane = std::atoi(v.c_str());
     else if (k == "spnb-load-mode") o.loadMode = std::atoi(v.c_str());
     else if (k == "spnb-stage-unroll") o.stageUnroll = std::atoi(v.c_str());
     else if (k == "spnb-tc-tiles") {
@@ -321,6 +322,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
     eo.scopeCut = opt.scopeCut;
     eo.hoistLoads = opt.hoistLoads;
     eo.loadAhead = opt.loadAhead;
+    eo.codePlane = opt.codePlane;
     eo.fuseLeaves = opt.fuseLeaves;
     eo.fuseEntries = opt.fuseEntries;
     eo.chunkBarrier = opt.chunkBarrier;
@@ -369,6 +371,7 @@ std::string Engine::compile(const std::string& queryPath, const Options& opt, co
   w.u64((uint64_t)ei.scratchSlots);
   w.u64((uint64_t)(ei.scoped ? 1 : 0));
   w.u64((uint64_t)ei.numChunks);
+  w.u64((uint64_t)ei.codePlaneBytes);
   w.u64((uint64_t)(jr.registers + 1));
   w.u64((uint64_t)(jr.spillBytes + 1));
   w.blob(xspn.data(), xspn.size());
@@ -500,6 +503,7 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->emitInfo_.scratchSlots = (int)r.u64();
   e->emitInfo_.scoped = r.u64() != 0;
   e->emitInfo_.numChunks = (int)r.u64();
+  e->emitInfo_.codePlaneBytes = (int)r.u64();
   int regs = (int)r.u64() - 1;
   int spill = (int)r.u64() - 1;
   std::vector<uint8_t> xspn = r.blob();
@@ -525,6 +529,7 @@ std::unique_ptr<Engine> Engine::load(const std::string& planPath) {
   e->tcFoldScalar_ = opt.tcFoldScalar;
   e->tcRings_ = opt.tcRings;
   e->tcGlobalSlots_ = opt.tcGlobalSlots;
+  e->bucketClamp_ = opt.bucketClamp != 0;
   // layered models run on the tensor-memory kernel unless another layered kernel is asked for by name
   e->layeredTcf_ = opt.kernelMode != "layered-scalar" && opt.kernelMode != "layered-mma";
   e->meta_.kernelName = e->model_.name;
@@ -623,6 +628,15 @@ Engine::DeviceState& Engine::state(int device) {
       st->crossBytes = st->scratchBytes;
       st->layeredChunkRows = 512 * 1024;
       st->scratchBytes += st->layeredChunkRows * (size_t)p.features.size() * 4;
+      if (emitInfo_.codePlaneBytes > 0) {
+        // ... and behind it the plane of staged codes of the discrete features, made by the same transposition
+        st->scratchBytes += st->layeredChunkRows * (size_t)p.numCodeSlots * (size_t)emitInfo_.codePlaneBytes;
+        std::vector<int4> meta(p.features.size());
+        for (size_t f = 0; f < meta.size(); ++f)
+          meta[f] = make_int4(p.features[f].lo, p.features[f].domain, p.features[f].codeSlot,
+                              bucketClamp_ && p.features[f].clampCodes ? 1 : 0);
+        st->dMeta = (int4*)upload(meta.data(), meta.size() * sizeof(int4));
+      }
     }
   } else if (strategy_ == kLayered) {
     LayeredPlan lp;
@@ -1044,7 +1058,11 @@ void Engine::launch(DeviceState& st, size_t n, const void* dIn, void* dOut, cuda
         unsigned long long ld = (rows + 255) / 256 * 256, nn = rows;
         const void* src = (const char*)dIn + r0 * rowBytes;
         void* dst = (char*)dOut + r0 * resBytes;
-        CUDA_OK(transposeInputs(dtypeCode(plan_.ftype), src, xt, rows, (int)meta_.numFeatures, ld, stream));
+        if (emitInfo_.codePlaneBytes > 0)
+          CUDA_OK(transposeInputsCoded((const float*)src, xt, xt + (size_t)meta_.numFeatures * ld, emitInfo_.codePlaneBytes,
+                                       st.dMeta, rows, (int)meta_.numFeatures, ld, stream));
+        else
+          CUDA_OK(transposeInputs(dtypeCode(plan_.ftype), src, xt, rows, (int)meta_.numFeatures, ld, stream));
         const size_t tilesC = (rows + (size_t)st.block - 1) / (size_t)st.block;
         const int gridC = (int)std::min<size_t>(tilesC, (size_t)st.grid);   // groups of tiles stride over the grid
         void* args[] = {(void*)&xt, (void*)&dst, (void*)&nn, (void*)&st.dTab, (void*)&st.dLut, (void*)&dScratch, (void*)&ld};

@@ -51,6 +51,7 @@ struct Options {
   int chunkBarrier = 0;        // "spnb-chunk-barrier": 1 = CTA-wide barriers around every chunk's staging with scope-local staging
   int fuseLeaves = 1;          // "spnb-fuse-leaves": fused tables for the discrete leaf children of a product
   int fuseEntries = 32;        // "spnb-fuse-entries": largest fused table, in entries
+  int codePlane = 1;           // "spnb-code-plane": 0 = scope-local staging digests discrete inputs itself
   int loadAhead = 0;           // "spnb-load-ahead": nodes between the request of an earlier chunk's value and its first use
   int hoistLoads = 0;          // "spnb-hoist-loads": operands of earlier chunks a scope-local chunk requests at its top
   int scopeBytes = 0;          // "spnb-scope-bytes": staged bytes per sample and chunk (0 = what fits)
@@ -119,6 +120,7 @@ class Engine {
   int tcFoldScalar_ = 0;
   int tcRings_ = 0;
   int tcGlobalSlots_ = -1;
+  bool bucketClamp_ = false;
   bool layeredTcf_ = false;
   std::string source_;
   std::vector<char> cubin_;

@@ -243,6 +243,37 @@ __global__ void transposeKernel(const in_t* __restrict__ in, float* __restrict__
     if (f < F && srow < ld) xt[(unsigned long long)f * ld + srow] = tileBuf[threadIdx.x][r];
   }
 }
+// float32 rows -> feature-major floats plus, for the discrete features, a feature-major plane of staged codes
+// (0 missing, 1 outside the domain, 2 + (x - lo) otherwise; with clamped special codes: 65535 / domain + 2):
+// codes[slot * ld + s], slot = meta[f].z (-1: no codes for this feature), meta[f] = (lo, domain, slot, clamped)
+template <typename code_t>
+__global__ void transposeCodedKernel(const float* __restrict__ in, float* __restrict__ xt, code_t* __restrict__ codes,
+                                     const int4* __restrict__ meta, unsigned long long n, int F, unsigned long long ld) {
+  __shared__ float tileBuf[32][33];
+  const unsigned long long s0 = (unsigned long long)blockIdx.x * 32;
+  const int f0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const unsigned long long srow = s0 + r;
+    const int f = f0 + threadIdx.x;
+    tileBuf[r][threadIdx.x] = (srow < n && f < F) ? in[srow * F + f] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int f = f0 + r;
+    const unsigned long long srow = s0 + threadIdx.x;
+    if (f < F && srow < ld) {
+      const float v = tileBuf[threadIdx.x][r];
+      xt[(unsigned long long)f * ld + srow] = v;
+      const int4 m = meta[f];
+      if (m.z >= 0) {
+        const unsigned rr = (unsigned)__float2int_rz(v) - (unsigned)m.x;
+        int code = rr < (unsigned)m.y ? (int)rr + 2 : (m.w ? m.y + 2 : 1);
+        if (v != v) code = m.w ? 65535 : 0;
+        codes[(unsigned long long)m.z * ld + srow] = (code_t)code;
+      }
+    }
+  }
+}
 template <typename in_t>
 cudaError_t transposeT(const void* in, float* xt, size_t n, int F, size_t ld, cudaStream_t stream) {
   dim3 grid((unsigned)((ld + 31) / 32), (unsigned)((F + 31) / 32)), block(32, 8);
@@ -265,6 +296,14 @@ cudaError_t transposeInputs(int dtypeCode, const void* in, float* xt, size_t n, 
     case DT_F64: return transposeT<double>(in, xt, n, F, ld, stream);
     default: return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t transposeInputsCoded(const float* in, float* xt, void* codes, int codeBytes, const int4* meta, size_t n, int F,
+                                 size_t ld, cudaStream_t stream) {
+  dim3 grid((unsigned)((ld + 31) / 32), (unsigned)((F + 31) / 32)), block(32, 8);
+  if (codeBytes == 1) transposeCodedKernel<unsigned char><<<grid, block, 0, stream>>>(in, xt, (unsigned char*)codes, meta, n, F, ld);
+  else transposeCodedKernel<unsigned short><<<grid, block, 0, stream>>>(in, xt, (unsigned short*)codes, meta, n, F, ld);
+  return cudaGetLastError();
 }
 
 size_t layeredSmemBytes(const LayeredArgs& a, int tile) {

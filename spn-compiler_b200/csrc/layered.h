@@ -53,6 +53,9 @@ size_t layeredSmemBytes(const LayeredArgs& a, int tile);
 // touch a different 32-byte sector per sample.
 cudaError_t transposeInputs(int dtypeCode, const void* in, float* xt, size_t n, int numFeatures, size_t ld,
                             cudaStream_t stream);
+// The same for float32 rows, plus a feature-major plane of staged codes for the discrete features (see layered.cu).
+cudaError_t transposeInputsCoded(const float* in, float* xt, void* codes, int codeBytes, const int4* meta, size_t n,
+                                 int numFeatures, size_t ld, cudaStream_t stream);
 cudaError_t layeredLaunch(const LayeredArgs& a, int dtypeCode, const void* in, float* out, size_t n, int grid, int tile,
                           size_t smem, cudaStream_t stream);
 cudaError_t layeredOccupancy(int tile, size_t smem, int* blocksPerSM);
