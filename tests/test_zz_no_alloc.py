@@ -17,7 +17,7 @@ from tests.util_models import REL_TOL_F32, max_rel_err, oracle_eval, small_confi
 pytestmark = pytest.mark.gpu
 
 
-def _both_entries(capi, plan, x):
+def _both_entries(capi, plan, x, warm=False):
     import torch
     n = x.shape[0]
     dx = torch.from_numpy(x).cuda()
@@ -27,6 +27,13 @@ def _both_entries(capi, plan, x):
     plan.execute_device(0, n, dx.data_ptr(), ref.data_ptr(), s)
     plan.execute_device_noalloc(0, n, dx.data_ptr(), got.data_ptr(), s)
     torch.cuda.synchronize()
+    if warm:
+        # the plan's image is resident now: another call must leave the device's free memory where it is
+        # (an allocation would show as 2 MiB or more)
+        free_before = torch.cuda.mem_get_info()[0]
+        plan.execute_device_noalloc(0, n, dx.data_ptr(), got.data_ptr(), s)
+        torch.cuda.synchronize()
+        assert free_before - torch.cuda.mem_get_info()[0] < (1 << 20)
     return got.cpu().numpy(), ref.cpu().numpy()
 
 
@@ -46,7 +53,7 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row(tmp_path):
         for name, q, inputs, plan, _ in plans:
             for call in range(2):     # two calls in a row share the array and what the first left in it
                 x = inputs(50001 + 1000 * call)
-                got, ref = _both_entries(capi, plan, x)
+                got, ref = _both_entries(capi, plan, x, warm=call == 1)
                 assert max_rel_err(got, ref) <= REL_TOL_F32, (name, rounds, call)
                 assert max_rel_err(got, oracle_eval(q, x, True)) <= REL_TOL_F32, (name, rounds, call)
     for _, _, _, plan, path in plans:
