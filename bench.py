@@ -59,7 +59,7 @@ CONFIGS = {
 # the samples of a launch)
 L2_FLUSH_BYTES = 256 * 2**20   # twice the 126 MB L2
 
-MEASURED_DRAM_BYTES_PER_SAMPLE = {1: 64.6, 2: 108.158, 3: 1234.5, 4: 35947.0, 5: 35818.0}
+MEASURED_DRAM_BYTES_PER_SAMPLE = {1: 64.6, 2: 108.158, 3: 1234.5, 4: 24721.0, 5: 35818.0}
 
 
 def make_model(cfg_id):

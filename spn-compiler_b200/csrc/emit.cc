@@ -946,11 +946,15 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "  const unsigned buf_s = (unsigned)__cvta_generic_to_shared(smem_raw);\n";
     o << "  uint4* win = reinterpret_cast<uint4*>(smem_raw + " << offTab << ");\n";
     o << "  unsigned tab_s = 0, lut_s = 0;\n";
-    o << "  const unsigned long long ntiles = (n + TILE - 1) / TILE;\n";
+    // Every CTA takes one contiguous range of rows (whole warps), in tiles of TILE rows, the last one partial: a
+    // batch of a few tiles per CTA then costs what its rows cost instead of a whole number of tile rounds (warps
+    // past the end of the range skip the body, which has no barrier in it).
+    o << "  const unsigned long long per = ((n + gridDim.x - 1) / gridDim.x + 31ull) & ~31ull;\n";
+    o << "  const unsigned long long lo = (unsigned long long)blockIdx.x * per;\n";
+    o << "  const unsigned long long hi = lo + per < n ? lo + per : n;\n";
     o << "  // copy of one tile: element e of the tile's row-major block goes to word (e / NF) * RS + e % NF\n";
-    o << "  auto issue = [&](unsigned long long tile, unsigned buf) {\n";
-    o << "    const unsigned long long base = tile * TILE;\n";
-    o << "    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
+    o << "  auto issue = [&](unsigned long long base, unsigned buf) {\n";
+    o << "    const unsigned rows = (hi - base) < (unsigned long long)TILE ? (unsigned)(hi - base) : (unsigned)TILE;\n";
     o << "    const in_t* __restrict__ src = in + base * NF;\n";
     o << "    const unsigned total = rows * NF;\n";
     o << "    const unsigned dst = buf_s + buf * " << asyncBuf << "u;\n";
@@ -961,7 +965,7 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     o << "    }\n";
     o << "    asm volatile(\"cp.async.commit_group;\" ::: \"memory\");\n";
     o << "  };\n";
-    o << "  if (blockIdx.x < ntiles) issue(blockIdx.x, 0u);\n";
+    o << "  if (lo < hi) issue(lo, 0u);\n";
     // (the tables are fetched while the first tile's copies are in flight)
     if (tabSmem) {
       // resident leaf tables behind the two buffers; the first barrier of the tile loop orders them before any read
@@ -974,17 +978,20 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
     }
     o << "  unsigned cur = 0;\n";
     o << "#pragma unroll 1\n";
-    o << "  for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {\n";
-    o << "    const unsigned long long base = tile * TILE;\n";
-    o << "    const unsigned rows = (n - base) < (unsigned long long)TILE ? (unsigned)(n - base) : (unsigned)TILE;\n";
+    o << "  for (unsigned long long base = lo; base < hi; base += TILE) {\n";
+    o << "    const unsigned rows = (hi - base) < (unsigned long long)TILE ? (unsigned)(hi - base) : (unsigned)TILE;\n";
     o << "    asm volatile(\"cp.async.wait_group 0;\" ::: \"memory\");\n";
     o << "    __syncthreads();   // this tile has landed for every thread; the other buffer's readers are done\n";
-    o << "    if (tile + gridDim.x < ntiles) issue(tile + gridDim.x, cur ^ 1u);\n";
+    o << "    if (base + TILE < hi) issue(base + TILE, cur ^ 1u);\n";
     o << "    const unsigned xs_s = buf_s + cur * " << asyncBuf << "u;\n";
-    o << "    out_t res;\n";
+    o << "    out_t res = (out_t)0;\n";
+    // the bodies hold no barrier (tables are resident) unless one was asked for
+    o << "    const bool active = " << (opt.syncEvery > 0 ? "true" : "(tid & ~31u) < rows") << ";\n";
     auto chainA = [&](const char* prefix, const std::string& in2) {
+      o << in2 << "if (active) {\n";
       for (size_t c = 0; c < nChunks; ++c)
-        o << in2 << (c + 1 == nChunks ? "res = " : "") << prefix << c << "(xs_s, 0u, tab_s, lut_s, tab_g, lut_g, win, sc, tid);\n";
+        o << in2 << "  " << (c + 1 == nChunks ? "res = " : "") << prefix << c << "(xs_s, 0u, tab_s, lut_s, tab_g, lut_g, win, sc, tid);\n";
+      o << in2 << "}\n";
     };
     if (twoBodies) {
       o << "    int nan = 0;\n";
