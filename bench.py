@@ -266,7 +266,7 @@ def run_reference(args, rank):
     whole = n == n_total
     sample = ("%s of the engine's batch (%d of %d samples) per step, all %d host threads; %s"
               % ("all" if whole else "a leading part", n, n_total, threads, CPU_PORT_NOTE))
-    print(json.dumps({
+    emit_result(({
         "impl": "reference", "metric": "SPN log-likelihood samples/sec", "value": val, "unit": "samples/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32" if cfg["log_space"] else "f64",
@@ -456,6 +456,26 @@ def e2e_host(w, steps, world, pinned):
     return dt, kernel_ms, same
 
 
+_RESULT_OUT = None
+
+
+def claim_stdout():
+    """The process's stdout carries the one JSON line and nothing else: whatever libraries print on file
+    descriptor 1 (NCCL's version banner, for one) is sent to stderr, the line goes out through a copy of the
+    original descriptor."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit_result(line):
+    claim_stdout()
+    _RESULT_OUT.write(json.dumps(line) + "\n")
+    _RESULT_OUT.flush()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -476,6 +496,7 @@ def main():
     if args.warm_plan_cache:
         warm_plan_cache()
         return
+    claim_stdout()
     per_config_wanted = args.config == 0 and not args.no_per_config and not args.samples and not args.opt
     args.config = args.config or 2
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -497,8 +518,6 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # NCCL writes its version banner (NCCL_DEBUG=VERSION and above) to stdout: stdout carries the JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cfg = CONFIGS[args.config]
     n_total = args.samples or cfg["n"]
@@ -606,7 +625,7 @@ def main():
         ww.close()
 
     if rank == 0:
-        print(json.dumps(line))
+        emit_result(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
