@@ -603,9 +603,10 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
   if (streamed && (chunk == 0 || groupTiles > 1)) swapWindow(o, winBase);
   std::vector<uint8_t> loaded(nChunks > 1 ? n : 0, 0);
   std::vector<std::string> terms;
-  if (scoped && nChunks > 1) {
+  if (scoped && nChunks > 1 && pfSlots == 0) {
     // Operands defined by earlier chunks: when they are few, all of them are requested at the top of the
     // function, so that their latencies (L2 or DRAM) overlap instead of standing in front of every first use.
+    // (Not together with the operand ring, which accounts for every operand of an earlier chunk itself.)
     std::vector<int32_t> incoming;
     for (size_t v = v0; v < v1; ++v)
       for (int64_t e = d.childPtr[v]; e < d.childPtr[v + 1]; ++e) {
