@@ -222,6 +222,33 @@ def test_discrete_leaves_of_a_product_share_a_fused_table(tmp_path):
     assert capi.Plan(small).stats["fused_table_entries"] == 36 + 20 + 20
 
 
+def test_staging_schemes_show_in_the_generated_source(tmp_path):
+    """Which staging scheme a model gets, read off the generated source.  (Compilation needs no GPU.)"""
+    from spnb import capi
+    configs = small_configs()
+    # 16 int32 features, discrete leaves: asynchronous double-buffered stage, codes digested in registers
+    name, spn, inputs, log_space, marginal = configs[0]
+    q = write_query(spn, marginal, directory=str(tmp_path))
+    plan = capi.Plan(capi.compile_query(q, {"target": "CUDA", "use-log-space": "false", "spnb-kernel": "unrolled"})[0])
+    assert "cp.async.ca.shared.global" in plan.source and "int cf0;" in plan.source and "ld.shared.u8" not in plan.source
+    sync = capi.Plan(capi.compile_query(q, {"target": "CUDA", "use-log-space": "false", "spnb-kernel": "unrolled",
+                                            "spnb-async-stage": "0"})[0])
+    assert "cp.async" not in sync.source and "ld.shared.u8" in sync.source
+    # 256 mixed features: scope-local staging, no CTA-wide barrier between chunks, codes from the byte plane
+    name, spn, inputs, log_space, marginal = configs[4]
+    q = write_query(spn, marginal, directory=str(tmp_path))
+    base = {"target": "CUDA", "use-log-space": "true", "spnb-kernel": "unrolled", "spnb-scoped": "1", "spnb-chunk-nodes": "300"}
+    plan = capi.Plan(capi.compile_query(q, base)[0])
+    assert plan.stats["scoped_staging"] and plan.stats["chunks"] > 5
+    assert "__any_sync(0xffffffffu, nan)" in plan.source and "__syncthreads_or(nan)" not in plan.source
+    assert "srcc[(unsigned long long)__ldg(cf + j) * ld]" in plan.source
+    lock = capi.Plan(capi.compile_query(q, dict(base, **{"spnb-chunk-barrier": "1", "spnb-code-plane": "0"}))[0])
+    assert "__syncthreads_or(nan)" in lock.source and "__any_sync" not in lock.source
+    assert "TOINT(raw)" in lock.source and "srcc[(unsigned long long)__ldg(cf + j) * ld]" not in lock.source
+    ring = capi.Plan(capi.compile_query(q, dict(base, **{"spnb-prefetch-slots": "4"}))[0])
+    assert "cp.async.wait_group 3; ld.shared.f32" in ring.source
+
+
 def test_two_tile_tensor_core_program(tmp_path):
     """The plan of a full-width layered model is annotated for the two-tile tensor-core kernel: right operands
     go straight to the operand buffer, left operands wait in registers (sibling = one leaf region) or in an
