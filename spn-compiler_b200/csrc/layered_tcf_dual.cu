@@ -12,7 +12,7 @@
 //     the MMAs of tile 0 and tile 1; warp 10 streams inner-region weights, warp 11 everything a leaf stage
 //     needs (its weights, the eight features' inputs for the 256 samples of the tile pair out of the
 //     feature-major copy, the eight centres) with bulk asynchronous copies (cp.async.bulk global -> shared,
-//     completion counted on an mbarrier; no multicast).  No worker thread loads inputs from global memory.
+//     completion counted on an mbarrier, this CTA only).  No worker thread loads inputs from global memory.
 //     Roles meet only through mbarriers; there is no CTA-wide barrier inside the tile loop.
 //   * A region's 32 outputs travel as a block normalised to a maximum of 1 plus one base-2 log scale per
 //     sample, which is what the consumer's contraction needs: inner regions take one logarithm per sample
