@@ -158,11 +158,11 @@ std::string makeStatsJson(const Plan& p, Strategy s, const EmitInfo& ei, int reg
 }
 
 void parallelCopy(void* dst, const void* src, size_t bytes) {
-  // up to half of the host's hardware threads (at most 12), 4 MB or more each: one thread moves about 5 GB/s,
+  // all but two of the host's hardware threads (at most 16), 2 MB or more each: one thread moves about 5 GB/s,
   // the copy engine behind it takes more than 50
-  const size_t kMin = 4u << 20;
-  const unsigned hw = std::max(8u, std::thread::hardware_concurrency());
-  unsigned nt = (unsigned)std::min<size_t>(std::min(12u, hw / 2), bytes / kMin);
+  const size_t kMin = 2u << 20;
+  const unsigned hw = std::max(6u, std::thread::hardware_concurrency());
+  unsigned nt = (unsigned)std::min<size_t>(std::min(16u, hw - 2), bytes / kMin);
   if (nt <= 1) {
     std::memcpy(dst, src, bytes);
     return;
