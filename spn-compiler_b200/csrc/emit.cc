@@ -177,7 +177,22 @@ std::string emitCuda(const Plan& p, const EmitOptions& opt, EmitInfo* info) {
       if (found) break;
     }
     if (!found) TILE = 64;
-    if (minBlocks <= 0) minBlocks = 1;
+    if (minBlocks <= 0) {
+      minBlocks = 1;
+      // A small model's code stays in the instruction cache, so nothing is gained by 32 warps walking it together;
+      // two CTAs of 512 threads per SM then do better than one of 1024: one stages or waits at a barrier while the
+      // other evaluates, and a batch's last round of tiles is half as coarse (352-node model, 1 M samples: 59.0 µs
+      // with one CTA of 1024 threads per SM, 55.2 with two of 512; a 2 000-node model loses 2 % that way).  Taken
+      // when both CTAs fit with either staging scheme (two buffers of raw rows, or staged slots plus tables).
+      const size_t half = (233472 / 2 - 1024);
+      const size_t rowsAsync = 2 * (((size_t)512 * (size_t)(d.numFeatures | 1) * 4 + 15) & ~size_t(15)) + 64;
+      const size_t rowsSync = fixed + 16 + (size_t)513 * perThread;
+      if (TILE == 1024 && n <= 1000 && opt.scoped != 1 && tabBytes <= (size_t)opt.smemTableLimit &&
+          std::max(rowsAsync, rowsSync) + tabBytes + 64 <= half) {
+        TILE = 512;
+        minBlocks = 2;
+      }
+    }
   } else if (minBlocks <= 0) {
     minBlocks = std::max(1, 1024 / TILE);
   }
